@@ -1,0 +1,80 @@
+"""ctypes binding of libna2d.so (the C ABI declared in include/na2d.h).
+
+There is no fallback: if the shared library is missing or does not load, importing this
+module raises, and every call that returns a non-zero status raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("NA2D_LIB", os.path.join(_PKG_DIR, "libna2d.so"))
+
+DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
+PATH_AUTO, PATH_SIMT, PATH_TENSOR = 0, 1, 2
+
+ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WINDOW, ERR_CUDA = -1, -2, -3, -4
+ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_KERNEL_WAIT = -5, -6, -7
+
+
+class Rows(C.Structure):
+    """Mirror of ``na2d_rows``: which global image rows the query-side and key-side tensors hold."""
+    _fields_ = [("q_row0", C.c_int), ("Hq", C.c_int), ("kv_row0", C.c_int), ("Hkv", C.c_int),
+                ("H_global", C.c_int)]
+
+
+# name -> (restype, argtypes); every symbol include/na2d.h declares
+SIGNATURES = {
+    "na2d_version": (C.c_int, []),
+    "na2d_strerror": (C.c_char_p, [C.c_int]),
+    "na2d_last_cuda_error": (C.c_char_p, []),
+    "na2d_window_start": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "na2d_backward_window": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "na2d_dump_index": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "na2d_forward": (C.c_int, [C.c_void_p] * 5 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
+    "na2d_backward_dq": (C.c_int, [C.c_void_p] * 8 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
+    "na2d_backward_dkdv": (C.c_int, [C.c_void_p] * 8 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
+    "na2d_backward": (C.c_int, [C.c_void_p] * 10 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
+    "na2d_check": (C.c_int, [C.c_int, C.c_void_p]),
+    "na2d_launch_count": (C.c_longlong, []),
+}
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built. Run "
+            "`python e_natten_b200/build.py` (needs nvcc); there is no CPU or PyTorch fallback.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise ImportError(f"{LIB_PATH} is stale (no symbol {name}); rebuild it with "
+                              "`python e_natten_b200/build.py --force`") from exc
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+class Na2dError(RuntimeError):
+    def __init__(self, status: int):
+        self.status = status
+        msg = lib.na2d_strerror(status).decode()
+        if status == ERR_CUDA:
+            msg += " -- " + lib.na2d_last_cuda_error().decode()
+        super().__init__(f"libna2d status {status}: {msg}")
+
+
+def check(status: int) -> None:
+    """Raise for a non-zero status: ValueError for argument problems, RuntimeError otherwise."""
+    if status == 0:
+        return
+    err = Na2dError(status)
+    if status in (ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WINDOW, ERR_TOO_LARGE):
+        raise ValueError(str(err))
+    raise err

@@ -1,0 +1,46 @@
+// Window index math shared by the host entry points and every kernel.
+//
+// These three functions are the bit-exact contract with e_natten: they restate
+// get_window_start (e_natten/pytorch.py:7-11, device twin e_natten/triton.py:7-12),
+// get_backward_window_start (e_natten/pytorch.py:13-17) and get_backward_window_end
+// (e_natten/pytorch.py:19-23) in integer arithmetic only.
+#pragma once
+
+#if defined(__CUDACC__)
+#define NA2D_HD __host__ __device__ __forceinline__
+#else
+#define NA2D_HD inline
+#endif
+
+// Origin of the kernel_size-wide window of pixel i on an axis of seq_len pixels: centred on
+// i, shifted inwards at the borders so that it never leaves the axis.
+NA2D_HD int na2d_ws(int i, int seq_len, int kernel_size) {
+    const int half = kernel_size / 2;
+    int start = i - half;
+    if (start < 0) start = 0;
+    if (i + half >= seq_len) start += seq_len - i - half - 1;
+    return start;
+}
+
+// First query index whose window holds key j.
+NA2D_HD int na2d_bws(int j, int kernel_size) {
+    return j < kernel_size ? 0 : j - kernel_size / 2;
+}
+
+// One past the last query index whose window holds key j.
+NA2D_HD int na2d_bwe(int j, int seq_len, int kernel_size) {
+    return j >= seq_len - kernel_size ? seq_len : j + kernel_size / 2 + 1;
+}
+
+// Geometry of one call, passed by value to every kernel.
+struct Na2dGeom {
+    int BN;        // batch * heads
+    int Hq;        // query-side rows held
+    int Hkv;       // key-side rows held
+    int W;         // grid columns
+    int C;         // head dim
+    int ks;        // kernel size (odd)
+    int q_row0;    // global row of query-side row 0
+    int kv_row0;   // global row of key-side row 0
+    int Hg;        // rows of the whole image
+};
