@@ -74,56 +74,59 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason sampler running beside the timed region."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only queries) from a
+    background thread, every few milliseconds, between start() and stop()."""
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+               "sw_power_cap": 0x4}
 
-    def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
-        self.lines = []
-        self.proc = None
-        self.thread = None
+    def __init__(self, uuid: str, period_s: float = 0.004):
+        self.uuid, self.period = uuid, period_s
+        self.samples, self.max_mhz, self.err = [], None, None
+        self._stop = threading.Event()
+        self._thread = None
+        self._window = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByUUID(self.uuid)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception as exc:                      # no NVML: report that, never guess
+            self.err = f"NVML unavailable: {exc}"
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
-        self.thread.start()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                self.samples.append((time.perf_counter(), float(mhz), int(mask)))
+            except Exception as exc:
+                self.err = str(exc)
+                return
+            time.sleep(self.period)
+
+    def mark(self, t0: float, t1: float):
+        """Host-clock window of the timed region; only samples inside it are reported."""
+        self._window = (t0, t1)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for nm, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(nm)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        if self.err and not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "samples": 0, "reasons": [self.err]}
+        sel = self.samples
+        if self._window:
+            sel = [x for x in self.samples if self._window[0] <= x[0] <= self._window[1]]
+        reasons = sorted(n for n, bit in self.REASONS.items() if any(x[2] & bit for x in sel))
+        return {"sm_mhz": statistics.median(x[1] for x in sel) if sel else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(sel), "reasons": reasons}
 
 
 # --------------------------------------------------------------------------------------- CPU arm
@@ -270,15 +273,17 @@ def main():
     barrier()
     na.check_kernels(dev)
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid))
     if rank == 0:
         sampler.start()
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     launches0 = na.launch_count()
     barrier()
+    t_host0 = time.perf_counter()
     for i in range(args.steps):
         step(evs[i])
     barrier()
+    sampler.mark(t_host0, time.perf_counter())
     launches = na.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     na.check_kernels(dev)

@@ -158,6 +158,24 @@ int simt_backward_dkdv(const Problem& p, const void* q, const void* k, const voi
 
 }  // namespace
 
+// Until the tcgen05 backward kernels are in place the 16-bit backward runs the SIMT kernels.
+namespace na2d_tc {
+int simt_dq_fallback(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const void* o,
+                     const float* lse, const void* d_o, void* d_q, float* delta, cudaStream_t st, int* launched) {
+    Problem p{g, dtype, false};
+    *launched += 0;   // counted by the SIMT launcher itself
+    return dtype == NA2D_BF16 ? simt_backward_dq<__nv_bfloat16>(p, q, k, v, o, lse, d_o, d_q, delta, st)
+                              : simt_backward_dq<__half>(p, q, k, v, o, lse, d_o, d_q, delta, st);
+}
+int simt_dkdv_fallback(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
+                       const void* d_o, const float* delta, void* d_k, void* d_v, cudaStream_t st, int* launched) {
+    Problem p{g, dtype, false};
+    *launched += 0;
+    return dtype == NA2D_BF16 ? simt_backward_dkdv<__nv_bfloat16>(p, q, k, v, lse, d_o, delta, d_k, d_v, st)
+                              : simt_backward_dkdv<__half>(p, q, k, v, lse, d_o, delta, d_k, d_v, st);
+}
+}  // namespace na2d_tc
+
 extern "C" {
 
 int na2d_version(void) { return 100; }

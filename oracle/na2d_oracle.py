@@ -132,7 +132,7 @@ def natten2d_fwd(q, k, v, kernel_size: int, acc_dtype=torch.float64, rows=None):
     return o, m + torch.log(l)
 
 
-def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=None):
+def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=None, o=None):
     """Backward in flash form.  Returns (dq, dk, dv) in ``acc_dtype``.
 
     p = exp(s - lse), delta = dO.O, dS = p*(dO.V - delta), dQ = sum dS*K,
@@ -141,13 +141,18 @@ def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=N
     neighbourhood of e_natten/pytorch.py:261-273 is implied, not re-derived).
     With ``rows`` (see _row_origins) dk / dv have the key band's shape and hold the partial
     sums over the local query band.
+
+    ``o`` is the forward output as the backward receives it.  The fused entry point saves o in
+    the input dtype (e_natten/triton.py:515), so on 16-bit paths the backward's input is the
+    rounded o; passing it here makes delta = dO.o use the same rounded values (rounding of an
+    input is not an error of the backward).  None uses the exact o.
     """
     B, N, H, W, C = q.shape
     Hkv = k.shape[2]
     ks = kernel_size
     q, k, v, d_o = (t.to(acc_dtype) for t in (q, k, v, d_o))
-    o, lse = natten2d_fwd(q, k, v, ks, acc_dtype, rows)
-    delta = (d_o * o).sum(-1)
+    o_exact, lse = natten2d_fwd(q, k, v, ks, acc_dtype, rows)
+    delta = (d_o * (o_exact if o is None else o.to(acc_dtype))).sum(-1)
     wsx, wsy = _row_origins(H, ks, rows), window_start_table(W, ks)
     dq = torch.zeros_like(q)
     dk = torch.zeros_like(k).view(B, N, Hkv * W, C)
@@ -165,10 +170,12 @@ def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=N
     return dq, dk.view(B, N, Hkv, W, C), dv.view(B, N, Hkv, W, C)
 
 
-def natten2d_fwd_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=None):
-    """(o, lse, dq, dk, dv) in one call."""
+def natten2d_fwd_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=None, save_dtype=None):
+    """(o, lse, dq, dk, dv) in one call.  ``save_dtype``: dtype in which o is handed to the
+    backward (the input dtype of a 16-bit path); None hands over the exact o."""
     o, lse = natten2d_fwd(q, k, v, kernel_size, acc_dtype, rows)
-    dq, dk, dv = natten2d_bwd(q, k, v, d_o, kernel_size, acc_dtype, rows)
+    o_saved = None if save_dtype is None else o.to(save_dtype)
+    dq, dk, dv = natten2d_bwd(q, k, v, d_o, kernel_size, acc_dtype, rows, o=o_saved)
     return o, lse, dq, dk, dv
 
 

@@ -25,7 +25,7 @@ def run_gpu(q, k, v, d_o, ks, path="auto", rows=None):
 def check_against_oracle(shape, ks, dtype, seed, path="auto", scale=1.0, q_scale=1.0):
     q, k, v, d_o = make_inputs(shape, dtype, seed, scale, q_scale)
     o, lse, dq, dk, dv = run_gpu(q, k, v, d_o, ks, path)
-    ro, rlse, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks)
+    ro, rlse, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks, save_dtype=dtype)
     tag = f"{tuple(shape)} ks={ks} {dtype} {path}"
     assert_close(o, ro, dtype, f"o {tag}")
     assert_close(lse, rlse, torch.float32 if dtype == torch.float32 else dtype, f"lse {tag}")
@@ -158,7 +158,7 @@ def _band_check(q, k, v, d_o, got, ks, bn_list, bands, dtype):
             kv1 = orc.window_start(e - 1, H, ks) + ks
             sl = lambda t, r0, r1: t[b:b + 1, n:n + 1, r0:r1].cpu()
             ro, rl, rdq, rdk, rdv = orc.natten2d_fwd_bwd(sl(q, a, e), sl(k, kv0, kv1), sl(v, kv0, kv1),
-                                                          sl(d_o, a, e), ks, rows=(a, kv0, H))
+                                                          sl(d_o, a, e), ks, rows=(a, kv0, H), save_dtype=dtype)
             tag = f"unit ({b},{n}) rows [{a},{e})"
             assert_close(sl(o, a, e), ro, dtype, "o " + tag)
             assert_close(sl(lse, a, e), rl, dtype, "lse " + tag)
@@ -222,7 +222,7 @@ def test_row_bands_reassemble_whole_image(dtype, path):
             assert_close(dqb, dq[:, :, a:e].double(), dtype, "band dq")
         dk_sum[:, :, kv0:kv1] += dkb.float()
         dv_sum[:, :, kv0:kv1] += dvb.float()
-    ro, rlse, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks)
+    ro, rlse, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks, save_dtype=dtype)
     assert_close(dk_sum, rdk, dtype, "sum of band dK partials")
     assert_close(dv_sum, rdv, dtype, "sum of band dV partials")
 
