@@ -118,14 +118,14 @@ int simt_forward(const Problem& p, const void* q, const void* k, const void* v, 
 }
 
 template <typename T>
-int simt_backward_dq(const Problem& p, const void* q, const void* k, const void* v, const void* o,
+int simt_backward_dq(const Problem& p, const void* q, const void* k, const void* v,
                      const float* lse, const void* d_o, void* d_q, float* delta, cudaStream_t st) {
     const Na2dGeom& g = p.g;
     const long long nq = (long long)g.BN * g.Hq * g.W;
     if (blocks_for(nq) > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
     na2d_simt::dq_kernel<T><<<(unsigned)blocks_for(nq), na2d_simt::kWarps * 32,
                               na2d_simt::dq_smem_bytes(g.C, g.ks), st>>>(
-        (const T*)q, (const T*)k, (const T*)v, (const T*)o, lse, (const T*)d_o, (T*)d_q, delta, g);
+        (const T*)q, (const T*)k, (const T*)v, lse, (const T*)d_o, (T*)d_q, delta, g);
     g_launches.fetch_add(1);
     NA2D_CUDA(cudaGetLastError());
     return NA2D_OK;
@@ -157,24 +157,6 @@ int simt_backward_dkdv(const Problem& p, const void* q, const void* k, const voi
     cudaStream_t st = (cudaStream_t)stream;
 
 }  // namespace
-
-// Until the tcgen05 backward kernels are in place the 16-bit backward runs the SIMT kernels.
-namespace na2d_tc {
-int simt_dq_fallback(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const void* o,
-                     const float* lse, const void* d_o, void* d_q, float* delta, cudaStream_t st, int* launched) {
-    Problem p{g, dtype, false};
-    *launched += 0;   // counted by the SIMT launcher itself
-    return dtype == NA2D_BF16 ? simt_backward_dq<__nv_bfloat16>(p, q, k, v, o, lse, d_o, d_q, delta, st)
-                              : simt_backward_dq<__half>(p, q, k, v, o, lse, d_o, d_q, delta, st);
-}
-int simt_dkdv_fallback(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-                       const void* d_o, const float* delta, void* d_k, void* d_v, cudaStream_t st, int* launched) {
-    Problem p{g, dtype, false};
-    *launched += 0;
-    return dtype == NA2D_BF16 ? simt_backward_dkdv<__nv_bfloat16>(p, q, k, v, lse, d_o, delta, d_k, d_v, st)
-                              : simt_backward_dkdv<__half>(p, q, k, v, lse, d_o, delta, d_k, d_v, st);
-}
-}  // namespace na2d_tc
 
 extern "C" {
 
@@ -240,7 +222,8 @@ int na2d_backward_dq(const void* q, const void* k, const void* v, const void* o,
                      const void* d_o, void* d_q, float* delta,
                      int B, int N, int H, int W, int C, int kernel_size, int dtype,
                      const na2d_rows* rows, int path, int device, void* stream) {
-    if (!q || !k || !v || !o || !lse || !d_o || !delta) return NA2D_ERR_BAD_ARG;
+    (void)o;   // not read: delta is formed as sum_j p_j dp_j, see the header
+    if (!q || !k || !v || !lse || !d_o || !delta) return NA2D_ERR_BAD_ARG;
     NA2D_ENTER();
     if (p.tensor) {
         int launched = 0;
@@ -250,9 +233,9 @@ int na2d_backward_dq(const void* q, const void* k, const void* v, const void* o,
         return rc;
     }
     switch (dtype) {
-        case NA2D_F32: return simt_backward_dq<float>(p, q, k, v, o, lse, d_o, d_q, delta, st);
-        case NA2D_BF16: return simt_backward_dq<__nv_bfloat16>(p, q, k, v, o, lse, d_o, d_q, delta, st);
-        default: return simt_backward_dq<__half>(p, q, k, v, o, lse, d_o, d_q, delta, st);
+        case NA2D_F32: return simt_backward_dq<float>(p, q, k, v, lse, d_o, d_q, delta, st);
+        case NA2D_BF16: return simt_backward_dq<__nv_bfloat16>(p, q, k, v, lse, d_o, d_q, delta, st);
+        default: return simt_backward_dq<__half>(p, q, k, v, lse, d_o, d_q, delta, st);
     }
 }
 

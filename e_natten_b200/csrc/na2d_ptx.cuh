@@ -162,8 +162,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
 // Instruction descriptor for kind::f16 (fp16 / bf16 inputs, fp32 accumulate).
 //   bits 4-5 D format (1 = f32); 7-9 A format, 10-12 B format (0 = f16, 1 = bf16);
 //   bit 15 A major, bit 16 B major (0 = K-major, 1 = MN-major); 17-22 N >> 3; 24-28 M >> 4.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool bf16, bool a_mn_major, bool b_mn_major) {
-    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
+// A and B carry their own format fields, but they must name the same type: an fp16 A with a
+// bf16 B raises an illegal-instruction fault on B200.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool a_bf16, bool b_bf16, bool a_mn_major,
+                                                  bool b_mn_major) {
+    return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) |
            ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
            (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }

@@ -8,7 +8,7 @@
 //
 // Math (what e_natten/triton.py:278-291 and 383-423 compute, the backward in flash form):
 //   s_j = q . k_j,  lse = max_j s_j + log sum_j exp(s_j - max),  p_j = exp(s_j - lse),
-//   o = sum_j p_j v_j;   delta = dO . o,  dp_j = dO . v_j,  ds_j = p_j (dp_j - delta),
+//   o = sum_j p_j v_j;   dp_j = dO . v_j,  delta = sum_j p_j dp_j (= dO . o),  ds_j = p_j (dp_j - delta),
 //   dQ = sum_j ds_j k_j,  dK_j += ds_j q,  dV_j += p_j dO   (+= over the inverse neighbourhood).
 #pragma once
 
@@ -48,7 +48,7 @@ __device__ __forceinline__ float warp_sum(float x) {
 
 // Dynamic shared memory per block, in bytes.
 inline size_t fwd_smem_bytes(int C, int ks) { return (size_t)kWarps * (C + ks * ks) * sizeof(float); }
-inline size_t dq_smem_bytes(int C, int ks) { return (size_t)kWarps * (2 * C + ks * ks) * sizeof(float); }
+inline size_t dq_smem_bytes(int C, int ks) { return (size_t)kWarps * (2 * C + 2 * ks * ks) * sizeof(float); }
 inline size_t dkdv_smem_bytes(int C) { return (size_t)kWarps * (2 * C + 64) * sizeof(float); }
 
 // ------------------------------------------------------------------------------------ forward
@@ -108,18 +108,21 @@ fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict
 }
 
 // ------------------------------------------------------------------------------------ dQ (+ delta)
+// delta = sum_j p_j dp_j, which equals dO . o exactly and does not depend on how o was rounded
+// when it was stored (the reference's backward does not read o either, e_natten/triton.py:522).
 // d_q may be null: then only delta is produced.
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 dq_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-          const T* __restrict__ o, const float* __restrict__ lse, const T* __restrict__ d_o,
+          const float* __restrict__ lse, const T* __restrict__ d_o,
           T* __restrict__ d_q, float* __restrict__ delta, Na2dGeom g) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nk = g.ks * g.ks;
-    float* qs = smem + warp * (2 * g.C + nk);
+    float* qs = smem + warp * (2 * g.C + 2 * nk);
     float* gs = qs + g.C;            // dO row
-    float* ds = gs + g.C;            // dS per window member
+    float* ps = gs + g.C;            // p per window member, then dS
+    float* dps = ps + nk;            // dP per window member
     const long long n_query = (long long)g.BN * g.Hq * g.W;
     const long long qi = (long long)blockIdx.x * kWarps + warp;
     if (qi >= n_query) return;
@@ -129,21 +132,16 @@ dq_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict_
     const int ox = na2d_ws(g.q_row0 + xl, g.Hg, g.ks) - g.kv_row0;
     const int oy = na2d_ws(y, g.W, g.ks);
 
-    float dl = 0.f;
     for (int c = lane; c < g.C; c += 32) {
-        const float go = to_f<T>(d_o[qi * g.C + c]);
         qs[c] = to_f<T>(q[qi * g.C + c]);
-        gs[c] = go;
-        dl = fmaf(go, to_f<T>(o[qi * g.C + c]), dl);
+        gs[c] = to_f<T>(d_o[qi * g.C + c]);
     }
-    dl = warp_sum(dl);
-    if (lane == 0) delta[qi] = dl;
-    if (d_q == nullptr) return;
     __syncwarp();
 
     const float row_lse = lse[qi];
     const T* kb = k + bn * g.Hkv * g.W * g.C;
     const T* vb = v + bn * g.Hkv * g.W * g.C;
+    float dl = 0.f;
     for (int j = lane; j < nk; j += 32) {
         const int u = j / g.ks, w = j - u * g.ks;
         const long long off = ((long long)(ox + u) * g.W + (oy + w)) * g.C;
@@ -155,15 +153,21 @@ dq_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict_
             dp = fmaf(gs[c], to_f<T>(vr[c]), dp);
         }
         const float p = expf(s - row_lse);
-        ds[j] = p * (dp - dl);
+        ps[j] = p;
+        dps[j] = dp;
+        dl = fmaf(p, dp, dl);
     }
+    dl = warp_sum(dl);
+    if (lane == 0) delta[qi] = dl;
+    if (d_q == nullptr) return;
+    for (int j = lane; j < nk; j += 32) ps[j] = ps[j] * (dps[j] - dl);
     __syncwarp();
     for (int c = lane; c < g.C; c += 32) {
         float acc = 0.f;
         int j = 0;
         for (int u = 0; u < g.ks; ++u) {
             const T* kr = kb + ((long long)(ox + u) * g.W + oy) * g.C + c;
-            for (int w = 0; w < g.ks; ++w, ++j) acc = fmaf(ds[j], to_f<T>(kr[(long long)w * g.C]), acc);
+            for (int w = 0; w < g.ks; ++w, ++j) acc = fmaf(ps[j], to_f<T>(kr[(long long)w * g.C]), acc);
         }
         d_q[qi * g.C + c] = from_f<T>(acc);
     }

@@ -35,11 +35,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 // Compile-time geometry of one (head dim, kernel size) instantiation.
-template <int D, int KS>
+// NMAX caps the keys (forward, dQ) or queries (dK/dV) of one chunk; it is set by how many
+// tensor-memory columns the kernel can spare for the S-shaped accumulators.
+template <int D, int KS, int NMAX = 256>
 struct Cfg {
     static constexpr int HH = TH + KS - 1;                 // halo box rows
     static constexpr int HW = TW + KS - 1;                 // halo box columns
-    static constexpr int RC_MAX = 256 / HW;
+    static constexpr int RC_MAX = NMAX / HW;
     static constexpr int NCH = (HH + RC_MAX - 1) / RC_MAX; // key chunks per tile
     static constexpr int RC = (HH + NCH - 1) / NCH;        // box rows per chunk
     static constexpr int NK = RC * HW;                     // keys per chunk
@@ -62,7 +64,7 @@ struct Cfg {
     static constexpr int TMEM_COLS = 512;
     static constexpr int SMEM_FWD = Q_BYTES + 2 * KV_BYTES + P_BYTES + 64 /*barriers*/ + 1024 /*alignment*/;
     static_assert(NB * 32 <= NPS * 64, "P slabs must hold every S block");
-    static_assert(NKP <= 256 && NKP % 16 == 0, "UMMA N range");
+    static_assert(NKP <= NMAX && NKP % 16 == 0, "UMMA N range");
     static_assert(KV_SLAB % 1024 == 0 && Q_SLAB % 1024 == 0, "slabs must keep the swizzle alignment");
 };
 
@@ -82,6 +84,17 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
 }
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Residual of a packed bf16 pair: packs (lo - value of the low half, hi - value of the high half).
+// dS is handed to its MMA as the bf16 pair (head, residual) on the bf16 path: a single bf16
+// keeps 8 significant bits, which leaves dQ / dK elements several 1e-2 off in the tails of a
+// large tensor; head + residual keeps 16.
+__device__ __forceinline__ uint32_t pack2_residual_bf16(float lo, float hi, uint32_t head) {
+    const float lo_head = __uint_as_float(head << 16);
+    const float hi_head = __uint_as_float(head & 0xffff0000u);
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo - lo_head, hi - hi_head);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
@@ -174,8 +187,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const int wr_lo = __shfl_sync(0xffffffffu, wr, 0);     // the warp's queries span box rows
     const int wr_hi = __shfl_sync(0xffffffffu, wr, 31);    //   [wr_lo, wr_hi + KS)
 
-    constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, false, false);
-    constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, false, true);
+    constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
+    constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
 
     float run_max = -CUDART_INF_F;      // running row maximum of s * log2(e)
     float run_sum = 0.f;                // running row sum of exp2(s * log2(e) - run_max)
@@ -434,19 +447,11 @@ inline int forward(const Na2dGeom& g, int dtype, const void* q, const void* k, c
     }
 }
 
-int simt_dq_fallback(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const void* o,
-                     const float* lse, const void* d_o, void* d_q, float* delta, cudaStream_t st, int* launched);
-int simt_dkdv_fallback(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-                       const void* d_o, const float* delta, void* d_k, void* d_v, cudaStream_t st, int* launched);
+}  // namespace na2d_tc
 
-inline int backward_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const void* o,
-                       const float* lse, const void* d_o, void* d_q, float* delta, int, cudaStream_t st, int* launched) {
-    return simt_dq_fallback(g, dtype, q, k, v, o, lse, d_o, d_q, delta, st, launched);
-}
-inline int backward_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-                         const void* d_o, const float* delta, void* d_k, void* d_v, int, cudaStream_t st, int* launched) {
-    return simt_dkdv_fallback(g, dtype, q, k, v, lse, d_o, delta, d_k, d_v, st, launched);
-}
+#include "na2d_tc_bwd.cuh"
+
+namespace na2d_tc {
 
 inline int read_and_clear_error(unsigned int* word, cudaStream_t st) {
     if (cudaMemcpyFromSymbolAsync(word, g_error_word, sizeof(unsigned int), 0, cudaMemcpyDeviceToHost, st) != cudaSuccess)

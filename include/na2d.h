@@ -94,9 +94,13 @@ int na2d_forward(const void* q, const void* k, const void* v, void* o, float* ls
                  int B, int N, int H, int W, int C, int kernel_size, int dtype,
                  const na2d_rows* rows, int path, int device, void* stream);
 
-/* Backward, query half: dQ (optional, may be NULL) and delta = rowsum(dO * o), fp32 of
- * B*N*Hq*W entries, which the key half reads.  Replaces the dQ part of Natten2d.backward +
- * _attn_bwd_2d (e_natten/triton.py:521-548, 383-409).  dQ is fully overwritten. */
+/* Backward, query half: dQ (optional, may be NULL) and the row delta, fp32 of B*N*Hq*W entries,
+ * which the key half reads.  delta is formed as sum_j p_j (dO . v_j), which equals dO . o
+ * exactly and is independent of the rounding o went through when it was stored; `o` is
+ * therefore accepted for interface symmetry but not read (it may be NULL), as in the reference,
+ * whose backward ignores the saved o (e_natten/triton.py:522).  Replaces the dQ part of
+ * Natten2d.backward + _attn_bwd_2d (e_natten/triton.py:521-548, 383-409).  dQ is fully
+ * overwritten. */
 int na2d_backward_dq(const void* q, const void* k, const void* v, const void* o, const float* lse,
                      const void* d_o, void* d_q, float* delta,
                      int B, int N, int H, int W, int C, int kernel_size, int dtype,
