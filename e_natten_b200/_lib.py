@@ -36,6 +36,7 @@ SIGNATURES = {
     "na2d_backward_dq": (C.c_int, [C.c_void_p] * 8 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
     "na2d_backward_dkdv": (C.c_int, [C.c_void_p] * 8 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
     "na2d_backward": (C.c_int, [C.c_void_p] * 10 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
+    "na2d_backward_static_scratch": (C.c_int, [C.c_void_p] * 9 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
     "na2d_check": (C.c_int, [C.c_int, C.c_void_p]),
     "na2d_launch_count": (C.c_longlong, []),
 }

@@ -145,6 +145,32 @@ int simt_backward_dkdv(const Problem& p, const void* q, const void* k, const voi
     return NA2D_OK;
 }
 
+// ---- scratch for na2d_backward_static_scratch ----------------------------------------------------
+// The backward pair passes the row delta from the dQ kernel to the dK/dV kernel through global
+// memory.  Normally the caller provides that buffer; the entry point below keeps it in this
+// file-scope device array instead, so that a caller who may not allocate can still run the
+// backward.  Every GPU that loads the library carries the array (4 MiB) until the process exits.
+constexpr long long kStaticDeltaFloats = 1LL << 20;
+static __device__ __align__(256) float g_static_delta[kStaticDeltaFloats];
+
+// Device address of g_static_delta on `device`, looked up once per device.  In host code the
+// name g_static_delta is only a handle for the runtime, not an address a kernel could use; the
+// address comes from cudaGetSymbolAddress, asked while `device` is the current device.
+int static_delta_address(int device, float** out) {
+    static std::mutex mu;
+    static float* cache[64];
+    if (device < 0 || device >= 64) return NA2D_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[device] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_delta);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_static_delta)");
+        cache[device] = static_cast<float*>(p);
+    }
+    *out = cache[device];
+    return NA2D_OK;
+}
+
 // Common prologue of the compute entry points: validate, select the device, check it.
 #define NA2D_ENTER()                                                                      \
     Problem p;                                                                            \
@@ -271,6 +297,32 @@ int na2d_backward(const void* q, const void* k, const void* v, const void* o, co
     if (rc != NA2D_OK || d_k == nullptr) return rc;
     return na2d_backward_dkdv(q, k, v, lse, d_o, delta, d_k, d_v, B, N, H, W, C, kernel_size, dtype,
                               rows, path, device, stream);
+}
+
+int na2d_backward_static_scratch(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                                 const void* d_o, void* d_q, void* d_k, void* d_v,
+                                 int B, int N, int H, int W, int C, int kernel_size, int dtype,
+                                 const na2d_rows* rows, int path, int device, void* stream) {
+    if (B <= 0 || N <= 0 || H <= 0 || W <= 0) return NA2D_ERR_BAD_ARG;
+    const long long hq = rows ? rows->Hq : H;
+    if (hq <= 0) return NA2D_ERR_BAD_ARG;
+    if ((long long)B * N * hq * W > kStaticDeltaFloats) {
+        snprintf(t_cuda_err, sizeof(t_cuda_err),
+                 "na2d_backward_static_scratch: B*N*Hq*W = %lld exceeds the built-in scratch of %lld floats",
+                 (long long)B * N * hq * W, kStaticDeltaFloats);
+        return NA2D_ERR_TOO_LARGE;
+    }
+    float* delta = nullptr;
+    {
+        DeviceScope scope(device);                        // the lookup needs `device` current
+        if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");
+        int rc = static_delta_address(device, &delta);
+        if (rc != NA2D_OK) return rc;
+    }
+    // delta is fully rewritten by the query half for every query of this call before the key
+    // half reads it, so nothing has to be cleared between calls.
+    return na2d_backward(q, k, v, o, lse, d_o, d_q, d_k, d_v, delta, B, N, H, W, C, kernel_size, dtype,
+                         rows, path, device, stream);
 }
 
 int na2d_check(int device, void* stream) {

@@ -125,6 +125,31 @@ int na2d_backward(const void* q, const void* k, const void* v, const void* o, co
                   int B, int N, int H, int W, int C, int kernel_size, int dtype,
                   const na2d_rows* rows, int path, int device, void* stream);
 
+/* Backward for callers that cannot allocate device memory.  No counterpart in the reference.
+ *
+ * Same computation and arguments as na2d_backward, minus `delta`: the B*N*Hq*W floats of row
+ * deltas that the dQ kernel hands to the dK/dV kernel live in an array built into the library
+ * (device memory reserved when the library is loaded, 4 MiB per GPU, held until the process
+ * exits).  It is meant for code that runs where cudaMalloc is off limits: a plugin inside a
+ * runtime whose arena already owns all of the GPU's memory and hands out no workspace, or a
+ * step that must not take the device-wide synchronisation that cudaMalloc / cudaFree imply.
+ * The call itself performs no cudaMalloc, cudaFree or other allocating call; inputs and outputs
+ * are still the caller's.
+ *
+ * Limits and rules:
+ *  - B*N*Hq*W <= NA2D_STATIC_SCRATCH_FLOATS (1,048,576; e.g. B4 N4 256x256).  Larger problems
+ *    return NA2D_ERR_TOO_LARGE (na2d_last_cuda_error() has the numbers); use na2d_backward.
+ *  - The first call on each device looks up the array's device address (a host-side runtime
+ *    query, no allocation).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Nothing in it needs clearing between calls
+ *    (every entry a call reads it has written first), but two calls whose kernels can overlap
+ *    on the GPU - different streams, no ordering between them - race on it.  Order them. */
+#define NA2D_STATIC_SCRATCH_FLOATS (1 << 20)
+int na2d_backward_static_scratch(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                                 const void* d_o, void* d_q, void* d_k, void* d_v,
+                                 int B, int N, int H, int W, int C, int kernel_size, int dtype,
+                                 const na2d_rows* rows, int path, int device, void* stream);
+
 /* Reads and clears the device-side error word that a kernel sets when a bounded wait
  * (mbarrier) ran out.  Synchronises the stream.  Returns NA2D_OK or NA2D_ERR_KERNEL_WAIT.
  * No reference counterpart. */
