@@ -18,8 +18,6 @@
 namespace na2d_tc {
 
 // ------------------------------------------------------------------------------------ dQ
-constexpr int kSmemLimit = 232448;     // dynamic shared memory a CTA can opt in to on sm_100
-
 template <int D, int KS, bool SPLIT>
 struct DqCfg : Cfg<D, KS, ((TH + KS - 1) * (TW + KS - 1) <= 256 ? 256 : 192)> {
     using B = Cfg<D, KS, ((TH + KS - 1) * (TW + KS - 1) <= 256 ? 256 : 192)>;
