@@ -1,9 +1,9 @@
 // tcgen05 tensor-core kernels for 2D neighborhood attention on sm_100a (bf16 / fp16 inputs,
 // fp32 accumulation), and their host-side launchers.
 //
-// Tiling.  A tile is 8 x 16 = 128 query pixels; query r of the tile is row r of every MMA and lane
+// Tiling.  A tile is TH x TW = 16 x 8 = 128 query pixels; query r of the tile is row r of every MMA and lane
 // r of tensor memory.  The keys a tile can see are the union of its pixels' clamped
-// windows: a (8+ks-1) x (16+ks-1) "halo box" whose origin is the window origin of the tile's
+// windows: a (TH+ks-1) x (TW+ks-1) "halo box" whose origin is the window origin of the tile's
 // first pixel.  The box is cut into chunks of whole box rows with at most 256 keys each (the
 // UMMA N limit); TMA brings each chunk of K and V into shared memory as [key][channel] rows with
 // the 128-byte (64-byte for head dim 32) swizzle, which is at once the K-major B operand of
@@ -28,8 +28,8 @@ namespace na2d_tc {
 
 using namespace na2d_ptx;
 
-constexpr int TH = 8;      // tile rows
-constexpr int TW = 16;     // tile columns
+constexpr int TH = 16;     // tile rows
+constexpr int TW = 8;      // tile columns (a warp covers 32 / TW tile rows)
 constexpr int TM = 128;    // queries (or keys) per tile = MMA M
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -37,10 +37,12 @@ constexpr float kLn2 = 0.6931471805599453f;
 // Compile-time geometry of one (head dim, kernel size) instantiation.
 // NMAX caps the keys (forward, dQ) or queries (dK/dV) of one chunk; it is set by how many
 // tensor-memory columns the kernel can spare for the S-shaped accumulators.
-template <int D, int KS, int NMAX = 256>
+// EXTRA_W widens the box (dK/dV: the inverse neighbourhood of a key tile whose first column is
+// below ks starts at column 0 and is up to ks/2 columns wider than TW + ks - 1).
+template <int D, int KS, int NMAX = 256, int EXTRA_W = 0>
 struct Cfg {
     static constexpr int HH = TH + KS - 1;                 // halo box rows
-    static constexpr int HW = TW + KS - 1;                 // halo box columns
+    static constexpr int HW = TW + KS - 1 + EXTRA_W;       // halo box columns
     static constexpr int RC_MAX = NMAX / HW;
     static constexpr int NCH = (HH + RC_MAX - 1) / RC_MAX; // key chunks per tile
     static constexpr int RC = (HH + NCH - 1) / NCH;        // box rows per chunk
@@ -64,7 +66,7 @@ struct Cfg {
     static constexpr int TMEM_COLS = 512;
     static constexpr int SMEM_FWD = Q_BYTES + 2 * KV_BYTES + P_BYTES + 64 /*barriers*/ + 1024 /*alignment*/;
     static_assert(NB * 32 <= NPS * 64, "P slabs must hold every S block");
-    static_assert(NKP <= NMAX && NKP % 16 == 0, "UMMA N range");
+    static_assert(NKP <= (NMAX + 15) / 16 * 16 && NKP % 16 == 0, "UMMA N range");
     static_assert(KV_SLAB % 1024 == 0 && Q_SLAB % 1024 == 0, "slabs must keep the swizzle alignment");
 };
 
@@ -100,6 +102,18 @@ __device__ __forceinline__ uint32_t pack2_residual_bf16(float lo, float hi, uint
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Writes 16 consecutive 16-bit values (packed in pairs) of row `row` of the same operand layout,
+// at columns [16*block16, 16*block16 + 16).
+__device__ __forceinline__ void store_operand_block16(uint32_t base, int slab_bytes, int row, int block16,
+                                                      const uint32_t (&w)[8]) {
+    const uint32_t row_base = base + (block16 >> 2) * slab_bytes + row * 128;
+#pragma unroll
+    for (int gI = 0; gI < 2; ++gI) {
+        const int chunk = ((block16 & 3) * 2 + gI) ^ (row & 7);
+        st_shared_v4(row_base + chunk * 16, w[4 * gI], w[4 * gI + 1], w[4 * gI + 2], w[4 * gI + 3]);
+    }
 }
 
 // Writes 32 consecutive 16-bit values (already packed in pairs) of row `row` of a K-major,

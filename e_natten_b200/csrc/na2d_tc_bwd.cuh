@@ -4,13 +4,13 @@
 // delta = sum_j p_j * dp_j (dp_j = dO . v_j), which equals dO . o exactly and does not depend on
 // how o was rounded when it was stored; the dQ kernel writes it to scratch for the dK/dV kernel.
 //
-// dQ kernel (one CTA per 8x16 query tile, rows = queries):
+// dQ kernel (one CTA per TH x TW query tile, rows = queries):
 //   phase A, per key chunk:  S = Q K^T, dP = dO V^T  ->  delta += sum_j p dp      (registers)
 //   phase B, per key chunk:  dS = p (dP - delta)  ->  shared  ->  dQ += dS K      (tensor memory)
 //   With a single chunk (ks <= 5) S and dP stay in tensor memory between the phases and dQ reuses
 //   the S columns; with several chunks phase B reloads the chunk and repeats the two MMAs.
 //
-// dK/dV kernel (one CTA per 8x16 key tile, rows = keys): the queries that can see the tile are
+// dK/dV kernel (one CTA per TH x TW key tile, rows = keys): the queries that can see the tile are
 //   the union of the keys' inverse neighbourhoods, a box of query pixels walked in chunks:
 //   S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T -> shared  ->  dV += P^T dO, dK += dS^T Q.
 #pragma once
@@ -99,7 +99,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 
-    const int qr_raw = r0 + (tid >> 4), qc_raw = c0 + (tid & 15);
+    const int qr_raw = r0 + (tid / TW), qc_raw = c0 + (tid % TW);
     const bool q_valid = qr_raw < g.Hq && qc_raw < g.W;
     const int qr = min(qr_raw, g.Hq - 1), qc = min(qc_raw, g.W - 1);
     const size_t qi = (static_cast<size_t>(bn) * g.Hq + qr) * g.W + qc;
@@ -338,8 +338,13 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     const int qb_r0 = max(na2d_bws(kg_first, KS), g.q_row0);                        // global row
     const int qb_r1 = min(na2d_bwe(kg_last, g.Hg, KS), g.q_row0 + g.Hq);
     const int n_rows = max(qb_r1 - qb_r0, 0);
-    const int n_ch = (n_rows + C::RC - 1) / C::RC;
+    // The box is walked in chunks of RC rows x HW columns.  Inside the image one column chunk is
+    // enough; where the inverse ranges are stretched by the clamping at both borders (first key
+    // column below ks and last one within ks of the right edge) the box is wider than HW and takes two.
     const int qb_c0 = na2d_bws(kc0, KS);
+    const int n_cols = na2d_bwe(min(kc0 + TW, g.W) - 1, g.W, KS) - qb_c0;
+    const int n_cc = (n_cols + C::HW - 1) / C::HW;
+    const int n_ch = ((n_rows + C::RC - 1) / C::RC) * n_cc;
     const int q_local_r0 = qb_r0 - g.q_row0;                                        // query-band row
 
     if (tid == 0) {
@@ -376,7 +381,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 
     // this thread's key and the queries that can see it, as bit masks over the query box
-    const int kr_raw = kr0 + (tid >> 4), kc_raw = kc0 + (tid & 15);
+    const int kr_raw = kr0 + (tid / TW), kc_raw = kc0 + (tid % TW);
     const bool k_valid = kr_raw < g.Hkv && kc_raw < g.W;
     const int kr = min(kr_raw, g.Hkv - 1), kc = min(kc_raw, g.W - 1);
     const size_t ki = (static_cast<size_t>(bn) * g.Hkv + kr) * g.W + kc;
@@ -392,8 +397,15 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         const uint32_t upto_hi = hi >= 32 ? 0xffffffffu : ((1u << hi) - 1u);
         return upto_hi & ~((1u << lo) - 1u);
     };
-    const uint32_t row_mask = range_mask(row_lo, row_hi);
-    const uint32_t col_mask = range_mask(col_lo, col_hi);
+    auto range_mask64 = [](int lo, int hi) -> uint64_t {      // the query box can be up to 40 rows tall
+        lo = max(lo, 0);
+        hi = min(hi, 64);
+        if (hi <= lo) return 0ull;
+        const uint64_t upto_hi = hi >= 64 ? ~0ull : ((1ull << hi) - 1ull);
+        return upto_hi & ~((1ull << lo) - 1ull);
+    };
+    const uint64_t row_mask = range_mask64(row_lo, row_hi);
+    const uint64_t col_mask64 = range_mask64(col_lo, col_hi);
     const int wrow_lo = __shfl_sync(0xffffffffu, row_lo, 0);     // the warp's keys are seen from box rows
     const int wrow_hi = __shfl_sync(0xffffffffu, row_hi, 31);    //   [wrow_lo, wrow_hi)
 
@@ -402,6 +414,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     uint32_t ph_load = 0, ph_s = 0, ph_o = 0;
 
     for (int ch = 0; ch < n_ch; ++ch) {
+        const int rc = ch / n_cc, cc = ch - rc * n_cc;          // row chunk, column chunk
         if (tid == 0) {
             if (ch > 0) {                       // the previous chunk's output MMAs still read sQ / sDO
                 mbar_wait(bar_o, ph_o, abort_flag, kErrMmaWait);
@@ -415,8 +428,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     tma_load_4d(sK + s * C::Q_SLAB, &tm_k, bar_load, s * 64, kc0, kr0, bn);
                     tma_load_4d(sV + s * C::Q_SLAB, &tm_v, bar_load, s * 64, kc0, kr0, bn);
                 }
-                tma_load_4d(sQ + s * C::KV_SLAB, &tm_q, bar_load, s * 64, qb_c0, q_local_r0 + ch * C::RC, bn);
-                tma_load_4d(sDO + s * C::KV_SLAB, &tm_do, bar_load, s * 64, qb_c0, q_local_r0 + ch * C::RC, bn);
+                tma_load_4d(sQ + s * C::KV_SLAB, &tm_q, bar_load, s * 64, qb_c0 + cc * C::HW, q_local_r0 + rc * C::RC, bn);
+                tma_load_4d(sDO + s * C::KV_SLAB, &tm_do, bar_load, s * 64, qb_c0 + cc * C::HW, q_local_r0 + rc * C::RC, bn);
             }
             mbar_wait(bar_load, ph_load, abort_flag, kErrLoadWait);
             ph_load ^= 1u;
@@ -447,8 +460,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         {
             float l2 = 0.f, dl = 0.f;
             if (tid < C::NK) {
-                const int br = ch * C::RC + tid / C::HW, bc = tid % C::HW;      // box row / column
-                const int qc = qb_c0 + bc;
+                const int br = rc * C::RC + tid / C::HW, bc = tid % C::HW;      // box row / column
+                const int qc = qb_c0 + cc * C::HW + bc;
                 if (br < n_rows && qc < g.W) {
                     const size_t qi = (static_cast<size_t>(bn) * g.Hq + (q_local_r0 + br)) * g.W + qc;
                     l2 = lse[qi] * kLog2e;
@@ -463,12 +476,13 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         ph_s ^= 1u;
         tc_fence_after();
 
-        const uint32_t rm = row_mask >> (ch * C::RC);
+        const uint32_t rm = static_cast<uint32_t>(row_mask >> (rc * C::RC));
+        const uint32_t col_mask = static_cast<uint32_t>(col_mask64 >> (cc * C::HW));
 #pragma unroll
         for (int b = 0; b < C::NB; ++b) {
-            const int row_first = ch * C::RC + (32 * b) / C::HW;
+            const int row_first = rc * C::RC + (32 * b) / C::HW;
             const int last_col = (32 * b + 31 < C::NK - 1) ? 32 * b + 31 : C::NK - 1;
-            const int row_last = ch * C::RC + last_col / C::HW;
+            const int row_last = rc * C::RC + last_col / C::HW;
             uint32_t wp[16], wd[16], wr2[16];
             if (32 * b < C::NK && row_last >= wrow_lo && row_first < wrow_hi) {      // warp-uniform
                 uint32_t s[32], dp[32];

@@ -1,56 +1,91 @@
 // Persistent, warp-specialised tcgen05 forward kernel.  Included by na2d_tc.cuh.
 //
-// One CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  A tile is 8 x 16 queries;
-// its halo box of keys is streamed in chunks of whole box rows with at most 128 keys.  Six warps:
-//   warps 0-3  softmax: read S from tensor memory, mask, online softmax, write P to shared
-//              memory; the output accumulates in tensor memory across the chunks of a tile and is
-//              rescaled there only when a row's maximum grows by more than 2^8 (until then the
-//              older maximum keeps being used, which leaves the result unchanged); store o, lse;
-//   warp 4     producer: TMA loads of Q tiles (two buffers) and K/V chunks (a ring of stages);
-//   warp 5     MMA issue: S = Q K^T into one of two S accumulators, O += P V into the tile's O
-//              accumulator (two, alternating by tile), with the S of the next chunk issued before
-//              the P V of the current one so that the tensor pipe and the softmax warps overlap.
-// Every hand-over is an mbarrier with a bounded wait.
+// One CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  A tile is TH x TW queries;
+// its halo box of keys is taken in chunks of whole box rows with at most 256 keys (one chunk for
+// kernel sizes up to 5).  Twelve warps in three groups of four:
+//   warps 0-7  softmax.  Warps w and w+4 own the same 32 queries (tensor-memory lanes
+//              32*(w%4)..) and split the 16-column blocks of S between them (even / odd); they
+//              read their blocks of S from tensor memory once, exchange the row maximum through
+//              shared memory, and write P back into tensor memory over S as packed 16-bit
+//              pairs, where it is the A operand of the second MMA.  The output accumulates in
+//              tensor memory across the chunks of a tile and is rescaled there only when a row's
+//              maximum grows by more than 2^8 (until then the older maximum keeps being used,
+//              which leaves the result unchanged).  The tile's epilogue (normalise, store o and
+//              lse) is deferred into the next tile, whose S MMA and loads it overlaps.
+//   warp 8     producer: TMA loads of Q tiles (two buffers), K chunks and V chunks (separate
+//              rings: a K slot is free again as soon as S = Q K^T has been computed);
+//   warp 9     MMA issue: S = Q K^T, then O += P V with P read from tensor memory;
+//   warps 10-11 idle (they fill the third group, which hands its registers to warps 0-7).
+// Shared-memory traffic is what the design economises: every UMMA with both operands in shared
+// memory re-reads a 128-row A operand, so S is computed with the widest N that fits and P never
+// touches shared memory.  Every hand-over is an mbarrier with a bounded wait.
 #pragma once
+
+#include <type_traits>
 
 namespace na2d_tc {
 
+#ifdef NA2D_TRACE
+// Development aid (not compiled into the shipped library): CTA 0 records the SM clock at the
+// hand-overs between the warps so that they can be laid out on a time line.
+__device__ unsigned long long g_trace[8192];     // [role 0..3][unit 0..255][event 0..7]
+__device__ unsigned int g_trace_n = 8192;
+__device__ __forceinline__ void trace(int role, int ev, unsigned n) {
+    if (blockIdx.x != 0 || n >= 256) return;
+    g_trace[(role * 256 + n) * 8 + ev] = clock64();
+}
+#define NA2D_TR(role, ev, n) trace(role, ev, n)
+#else
+#define NA2D_TR(role, ev, n)
+#endif
+
 template <int D, int KS>
-struct FwdCfg : Cfg<D, KS, 128> {
-    using B = Cfg<D, KS, 128>;
-    static constexpr int STAGE_BYTES = 2 * B::KV_BYTES;                 // K chunk then V chunk
-    static constexpr int FIXED = 2 * B::Q_BYTES + B::P_BYTES + 256 /*barriers*/ + 1024 /*alignment*/;
-    static constexpr int NST_FIT = (kSmemLimit - FIXED) / STAGE_BYTES;
-    static constexpr int NST = NST_FIT > 4 ? 4 : NST_FIT;               // K/V ring depth
-    static constexpr int SMEM = FIXED + NST * STAGE_BYTES;
-    static constexpr int TMEM_S0 = 0, TMEM_O0 = 256, TMEM_STRIDE = 128; // S[2] at 0/128, O[2] at 256/384
-    static_assert(NST >= 2, "forward kernel needs at least two K/V stages");
-    static_assert(B::NKP <= 128 && D <= 128, "tensor memory layout");
+struct FwdCfg : Cfg<D, KS, 256> {
+    using B = Cfg<D, KS, 256>;
+    // The K chunk keeps only the rows TMA writes (rounded to the swizzle period): the UMMA reads
+    // NKP rows, and the few it reads past the end only feed S columns that are masked anyway.
+    // The V chunk keeps all NKP rows, the padding ones zeroed, because they are contraction rows.
+    static constexpr int K_ROWS = B::ROWB == 128 ? (B::NK + 7) / 8 * 8 : B::NKP;
+    static constexpr int K_SLAB = K_ROWS * B::ROWB;
+    static constexpr int K_BYTES = B::NS * K_SLAB;
+    static constexpr int V_BYTES = B::KV_BYTES;
+    static constexpr int XCHG_BYTES = 4 * 2 * 128 * 4;                  // row max [2][2][128], row sum [2][2][128]
+    static constexpr int FIXED = 2 * B::Q_BYTES + XCHG_BYTES + 256 /*barriers*/ + 1024 /*alignment*/;
+    static constexpr int NSTAGE = (FIXED + 2 * (K_BYTES + V_BYTES) <= kSmemLimit) ? 2 : 1;   // K and V ring depth
+    static constexpr int SMEM = FIXED + NSTAGE * (K_BYTES + V_BYTES);
+    static constexpr int NB16 = (B::NKP + 15) / 16;                     // 16-column blocks of S
+    static constexpr int TMEM_S = 0, TMEM_O0 = 256, TMEM_OSTRIDE = 128; // S / P at 0, O[2] at 256 / 384
+    static_assert(SMEM <= kSmemLimit, "forward kernel shared memory");
+    static_assert(B::NKP <= 256 && D <= 128, "tensor memory layout");
 };
 
 template <typename DT, int D, int KS>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, DT* __restrict__ o, float* __restrict__ lse,
            const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
     using C = FwdCfg<D, KS>;
+    constexpr int NST = C::NSTAGE;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;                                   // 2 x Q tile
-    uint8_t* sKV = sQ + 2 * C::Q_BYTES;                   // NST x (K chunk, V chunk)
-    uint8_t* sP = sKV + C::NST * C::STAGE_BYTES;          // P of the current chunk
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::P_BYTES);
+    uint8_t* sK = sQ + 2 * C::Q_BYTES;                    // NST x K chunk
+    uint8_t* sV = sK + NST * C::K_BYTES;                  // NST x V chunk
+    float* x_max = reinterpret_cast<float*>(sV + NST * C::V_BYTES);   // [unit parity][half][row]
+    float* x_sum = x_max + 2 * 2 * 128;                               // [tile parity][half][row]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_sum + 2 * 2 * 128);
     uint64_t* q_full = bars;                 // [2]   TMA -> MMA
     uint64_t* q_empty = bars + 2;            // [2]   MMA (commit) -> TMA
-    uint64_t* s_full = bars + 4;             // [2]   MMA (commit) -> softmax
-    uint64_t* s_free = bars + 6;             // [2]   softmax -> MMA
-    uint64_t* o_full = bars + 8;             // [2]   MMA (commit) -> softmax
-    uint64_t* o_free = bars + 10;            // [2]   softmax -> MMA
-    uint64_t* p_full = bars + 12;            //       softmax -> MMA
-    uint64_t* p_free = bars + 13;            //       MMA (commit) -> softmax
-    uint64_t* kv_full = bars + 14;           // [NST] TMA -> MMA
-    uint64_t* kv_empty = bars + 14 + C::NST; // [NST] MMA (commit) -> TMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14 + 2 * C::NST);
+    uint64_t* o_full = bars + 4;             // [2]   MMA (commit) -> softmax
+    uint64_t* o_free = bars + 6;             // [2]   softmax -> MMA
+    uint64_t* k_full = bars + 8;             // [2]   TMA -> MMA
+    uint64_t* k_empty = bars + 10;           // [2]   MMA (commit) -> TMA
+    uint64_t* v_full = bars + 12;            // [2]   TMA -> MMA
+    uint64_t* v_empty = bars + 14;           // [2]   MMA (commit) -> TMA
+    uint64_t* s_full = bars + 16;            //       MMA (commit) -> softmax
+    uint64_t* p_full = bars + 17;            //       softmax -> MMA
+    uint64_t* pv_done = bars + 18;           //       MMA (commit) -> softmax: O holds this chunk
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -62,17 +97,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int i = 0; i < 2; ++i) {
             mbar_init(q_full + i, 1);
             mbar_init(q_empty + i, 1);
-            mbar_init(s_full + i, 1);
-            mbar_init(s_free + i, 4);
             mbar_init(o_full + i, 1);
-            mbar_init(o_free + i, 4);
+            mbar_init(o_free + i, 8);
+            mbar_init(k_full + i, 1);
+            mbar_init(k_empty + i, 1);
+            mbar_init(v_full + i, 1);
+            mbar_init(v_empty + i, 1);
         }
-        mbar_init(p_full, 4);
-        mbar_init(p_free, 1);
-        for (int i = 0; i < C::NST; ++i) {
-            mbar_init(kv_full + i, 1);
-            mbar_init(kv_empty + i, 1);
-        }
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 8);
+        mbar_init(pv_done, 1);
         mbar_fence_init();
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_k);
@@ -86,10 +120,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // V rows [NK, NKP) of every stage are contraction rows of P V that TMA never writes.
     if constexpr (C::NKP > C::NK) {
         constexpr int pad16 = (C::NKP - C::NK) * C::ROWB / 16;
-        for (int i = tid; i < C::NST * C::NS * pad16; i += 192) {
+        for (int i = tid; i < NST * C::NS * pad16; i += 384) {
             const int which = i / pad16, off = i - which * pad16;
             const int st = which / C::NS, slab = which % C::NS;
-            uint8_t* base = sKV + st * C::STAGE_BYTES + C::KV_BYTES + slab * C::KV_SLAB;
+            uint8_t* base = sV + st * C::V_BYTES + slab * C::KV_SLAB;
             st_shared_v4(smem_u32(base + C::NK * C::ROWB + off * 16), 0u, 0u, 0u, 0u);
         }
         fence_proxy_async();
@@ -108,8 +142,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         bn = t / tiles_r;
     };
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------------ producer
+        reg_dec<64>();
         if (lane == 0) {
             uint32_t n = 0;
             for (int i = 0; i < n_my; ++i) {
@@ -124,65 +159,85 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 for (int s = 0; s < C::NS; ++s)
                     tma_load_4d(sQ + qb * C::Q_BYTES + s * C::Q_SLAB, &tm_q, q_full + qb, s * 64, c0, r0, bn);
                 for (int c = 0; c < C::NCH; ++c, ++n) {
-                    const uint32_t st = n % C::NST;
-                    mbar_wait(kv_empty + st, ((n / C::NST) & 1) ^ 1, abort_flag, kErrLoadWait);
-                    mbar_expect_tx(kv_full + st, 2u * C::NS * C::NK * C::ROWB);
-                    uint8_t* dst = sKV + st * C::STAGE_BYTES;
+                    const uint32_t st = n % NST, ph = ((n / NST) & 1) ^ 1;
+                    NA2D_TR(1, 0, n);
+                    mbar_wait(k_empty + st, ph, abort_flag, kErrLoadWait);
+                    NA2D_TR(1, 1, n);
+                    mbar_expect_tx(k_full + st, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
-                    for (int s = 0; s < C::NS; ++s) {
-                        tma_load_4d(dst + s * C::KV_SLAB, &tm_k, kv_full + st, s * 64, box_c0, box_r0 + c * C::RC, bn);
-                        tma_load_4d(dst + C::KV_BYTES + s * C::KV_SLAB, &tm_v, kv_full + st, s * 64, box_c0,
+                    for (int s = 0; s < C::NS; ++s)
+                        tma_load_4d(sK + st * C::K_BYTES + s * C::K_SLAB, &tm_k, k_full + st, s * 64, box_c0,
                                     box_r0 + c * C::RC, bn);
-                    }
+                    mbar_wait(v_empty + st, ph, abort_flag, kErrLoadWait);
+                    NA2D_TR(1, 2, n);
+                    mbar_expect_tx(v_full + st, (uint32_t)C::NS * C::NK * C::ROWB);
+#pragma unroll
+                    for (int s = 0; s < C::NS; ++s)
+                        tma_load_4d(sV + st * C::V_BYTES + s * C::KV_SLAB, &tm_v, v_full + st, s * 64, box_c0,
+                                    box_r0 + c * C::RC, bn);
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
-            constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
-            auto issue_s = [&](uint32_t n) {
-                const uint32_t i = n / C::NCH, c = n % C::NCH, st = n % C::NST, sb = n & 1;
-                if (c == 0) mbar_wait(q_full + (i & 1), (i >> 1) & 1, abort_flag, kErrLoadWait);
-                mbar_wait(kv_full + st, (n / C::NST) & 1, abort_flag, kErrLoadWait);
-                mbar_wait(s_free + sb, ((n >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
-                tc_fence_after();
-                const uint32_t q_addr = smem_u32(sQ + (i & 1) * C::Q_BYTES);
-                const uint32_t k_addr = smem_u32(sKV + st * C::STAGE_BYTES);
+        // (the whole warp walks the loop so that addresses stay warp-uniform; one lane issues)
+        reg_dec<64>();
+        const bool leader = lane == 0;
+        constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
+        constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
+        constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
+        for (uint32_t n = 0; n < total_units; ++n) {
+            const uint32_t i = n / C::NCH, c = n % C::NCH, st = n % NST, ph = (n / NST) & 1, ob = i & 1;
+            if (lane == 0) NA2D_TR(2, 0, n);
+            if (c == 0) mbar_wait(q_full + (i & 1), (i >> 1) & 1, abort_flag, kErrLoadWait);
+            mbar_wait(k_full + st, ph, abort_flag, kErrLoadWait);
+            if (lane == 0) NA2D_TR(2, 1, n);
+            tc_fence_after();
+            const uint32_t q_lo = smem_desc_lo(smem_u32(sQ + (i & 1) * C::Q_BYTES), 16);
+            const uint32_t k_lo = smem_desc_lo(smem_u32(sK + st * C::K_BYTES), 16);
+            if (leader) {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const int slab = (kk * 16) / C::SLAB_C, in_slab = (kk * 16) % C::SLAB_C;
-                    const uint64_t a = smem_desc(q_addr + slab * C::Q_SLAB + in_slab * 2, 16, C::ATOM, C::SWZ);
-                    const uint64_t b = smem_desc(k_addr + slab * C::KV_SLAB + in_slab * 2, 16, C::ATOM, C::SWZ);
-                    umma_ss(tmem_base + C::TMEM_S0 + sb * C::TMEM_STRIDE, a, b, idesc_s, kk > 0);
+                    constexpr int kPerSlab = C::SLAB_C / 16;
+                    const int slab = kk / kPerSlab, in_slab = kk % kPerSlab;
+                    umma_ss(tmem_base + C::TMEM_S, desc64(hi, q_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
+                            desc64(hi, k_lo + ((slab * C::K_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
                 }
-                umma_commit(s_full + sb);
+                umma_commit(s_full);
+                umma_commit(k_empty + st);
                 if (c == C::NCH - 1) umma_commit(q_empty + (i & 1));      // the tile's Q buffer is free
-            };
-            if (total_units > 0) issue_s(0);
-            for (uint32_t n = 0; n < total_units; ++n) {
-                if (n + 1 < total_units) issue_s(n + 1);
-                const uint32_t i = n / C::NCH, c = n % C::NCH, st = n % C::NST, ob = i & 1;
-                mbar_wait(p_full, n & 1, abort_flag, kErrMmaWait);
-                if (c == 0) mbar_wait(o_free + ob, ((i >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(sKV + st * C::STAGE_BYTES + C::KV_BYTES);
+            }
+            __syncwarp();
+            if (lane == 0) NA2D_TR(2, 2, n);
+            mbar_wait(v_full + st, ph, abort_flag, kErrLoadWait);
+            mbar_wait(p_full, n & 1, abort_flag, kErrMmaWait);
+            if (lane == 0) NA2D_TR(2, 3, n);
+            if (c == 0) mbar_wait(o_free + ob, ((i >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
+            tc_fence_after();
+            const uint32_t v_lo = smem_desc_lo(smem_u32(sV + st * C::V_BYTES), C::KV_SLAB);
+            if (leader) {
 #pragma unroll
                 for (int kk = 0; kk < C::NKP / 16; ++kk) {
-                    const uint64_t a = smem_desc(smem_u32(sP + (kk >> 2) * C::P_SLAB) + (kk & 3) * 32, 16, 1024, 2u);
-                    const uint64_t b = smem_desc(v_addr + kk * 16 * C::ROWB, C::KV_SLAB, C::ATOM, C::SWZ);
-                    umma_ss(tmem_base + C::TMEM_O0 + ob * C::TMEM_STRIDE, a, b, idesc_o, (c > 0) || (kk > 0));
+                    umma_ts(tmem_base + C::TMEM_O0 + ob * C::TMEM_OSTRIDE, tmem_base + C::TMEM_S + 8 * kk,
+                            desc64(hi, v_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, (c > 0) || (kk > 0));
                 }
-                umma_commit(kv_empty + st);
-                umma_commit(p_free);                       // also: "this chunk's P V has landed in O"
+                umma_commit(v_empty + st);
+                umma_commit(pv_done);
                 if (c == C::NCH - 1) umma_commit(o_full + ob);
             }
+            __syncwarp();
+            if (lane == 0) NA2D_TR(2, 4, n);
         }
+    } else if (warp >= 10) {
+        reg_dec<64>();                 // spare warps of the data-movement group
     } else {
         // ------------------------------------------------------------------ softmax warps
-        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+        reg_inc<216>();
+        const int quarter = warp & 3, half = warp >> 2;
+        const int row = quarter * 32 + lane;                 // query of the tile = tensor-memory lane
+        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         constexpr float kRescaleStep = 8.f;      // log2 units: rescale O when the maximum grows by > 2^8
+        constexpr int DH = D / 2;                // output columns of this half
         // epilogue of the previous tile, deferred until the next tile's first chunk is under way
         bool pend = false, pend_valid = false;
         uint32_t pend_tile = 0;
@@ -191,31 +246,33 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
         auto epilogue = [&]() {
             const uint32_t ob = pend_tile & 1;
+            bar_sync(1 + quarter, 64);                                       // partner's row sum is in x_sum
+            const float total = pend_sum + x_sum[((pend_tile & 1) * 2 + (half ^ 1)) * 128 + row];
             mbar_wait(o_full + ob, (pend_tile >> 1) & 1, abort_flag, kErrMmaWait);
             tc_fence_after();
-            const float inv = 1.f / pend_sum;
-            DT* orow = o + pend_qi * D;
+            const float inv = 1.f / total;
+            DT* orow = o + pend_qi * D + half * DH;
 #pragma unroll
-            for (int piece = 0; piece < D / 32; ++piece) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_lane + C::TMEM_O0 + ob * C::TMEM_STRIDE + 32 * piece, v);
+            for (int piece = 0; piece < DH / 16; ++piece) {
+                uint32_t v[16];
+                tmem_ld_32x16(tmem_lane + C::TMEM_O0 + ob * C::TMEM_OSTRIDE + half * DH + 16 * piece, v);
                 tmem_ld_wait();
                 if (pend_valid) {
 #pragma unroll
-                    for (int gI = 0; gI < 4; ++gI) {
+                    for (int gI = 0; gI < 2; ++gI) {
                         uint4 pk;
                         pk.x = pack2<DT>(__uint_as_float(v[8 * gI + 0]) * inv, __uint_as_float(v[8 * gI + 1]) * inv);
                         pk.y = pack2<DT>(__uint_as_float(v[8 * gI + 2]) * inv, __uint_as_float(v[8 * gI + 3]) * inv);
                         pk.z = pack2<DT>(__uint_as_float(v[8 * gI + 4]) * inv, __uint_as_float(v[8 * gI + 5]) * inv);
                         pk.w = pack2<DT>(__uint_as_float(v[8 * gI + 6]) * inv, __uint_as_float(v[8 * gI + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + 32 * piece + 8 * gI) = pk;
+                        *reinterpret_cast<uint4*>(orow + 16 * piece + 8 * gI) = pk;
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(o_free + ob);
-            if (pend_valid) lse[pend_qi] = (pend_max + log2f(pend_sum)) * kLn2;
+            if (pend_valid && half == 0) lse[pend_qi] = (pend_max + log2f(total)) * kLn2;
             pend = false;
         };
 
@@ -225,7 +282,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             decode(i, bn, r0, c0);
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
-            const int qr_raw = r0 + (tid / TW), qc_raw = c0 + (tid % TW);
+            const int qr_raw = r0 + (row / TW), qc_raw = c0 + (row % TW);
             const bool q_valid = qr_raw < g.Hq && qc_raw < g.W;
             const int qr = min(qr_raw, g.Hq - 1), qc = min(qc_raw, g.W - 1);
             const int wr = na2d_ws(g.q_row0 + qr, g.Hg, KS) - g.kv_row0 - box_r0;   // in [0, TH)
@@ -234,111 +291,146 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const uint32_t col_mask = ((1u << KS) - 1u) << wc;
             const int wr_lo = __shfl_sync(0xffffffffu, wr, 0);
             const int wr_hi = __shfl_sync(0xffffffffu, wr, 31);
-            const uint32_t o_addr = tmem_lane + C::TMEM_O0 + (i & 1) * C::TMEM_STRIDE;
-            float run_max = -CUDART_INF_F, run_sum = 0.f;
+            const uint32_t o_addr = tmem_lane + C::TMEM_O0 + (i & 1) * C::TMEM_OSTRIDE + half * DH;
+            float run_max = -CUDART_INF_F, run_sum = 0.f;        // run_sum: this half's columns only
 
-            for (int ch = 0; ch < C::NCH; ++ch, ++n) {
-                const uint32_t sb = n & 1;
-                const uint32_t s_addr = tmem_lane + C::TMEM_S0 + sb * C::TMEM_STRIDE;
-                const uint32_t rm = row_mask >> (ch * C::RC);            // bit r: chunk row r is in the window
-                mbar_wait(s_full + sb, (n >> 1) & 1, abort_flag, kErrMmaWait);
+            // One chunk.  The warp's queries can only see a contiguous range of the chunk's columns
+            // (box rows wr_lo .. wr_hi + ks); of the 16-column blocks in that range this warp takes
+            // every other one, at most NACT of them, reads each once into registers and keeps a
+            // 16-bit validity mask per block (built from the query's ks window rows) beside it.
+            auto unit = [&](const int ch) {
+                constexpr int NBH = (C::NB16 + 1) / 2;                      // own blocks at most
+                constexpr int kRows = (32 / TW - 1 + KS) < C::RC ? (32 / TW - 1 + KS) : C::RC;
+                constexpr int kBlocks = (kRows * C::HW - 1) / 16 + 2;
+                constexpr int NACT = (kBlocks + 1) / 2 < NBH ? (kBlocks + 1) / 2 : NBH;
+                const uint32_t s_addr = tmem_lane + C::TMEM_S;
+                const int row_off = ch * C::RC;
+                const int j_lo = max(wr_lo - row_off, 0) * C::HW;
+                const int j_hi = min(min(wr_hi + KS - row_off, C::RC) * C::HW, C::NK);       // exclusive
+                const int b_hi = (max(j_hi, 0) + 15) >> 4;                                   // blocks [j_lo/16, b_hi)
+                const int bi_lo = ((j_lo >> 4) - half + 1) >> 1;                             // first own block in range
+                if (tid == 0) NA2D_TR(3, 0, n);
+                mbar_wait(s_full, n & 1, abort_flag, kErrMmaWait);
+                if (tid == 0) NA2D_TR(3, 1, n);
                 tc_fence_after();
 
-                // pass 1: masked maximum of the chunk
-                float cmax = -CUDART_INF_F;
+                uint32_t s[NACT][16];
+                uint32_t vmask[NACT];
 #pragma unroll
-                for (int b = 0; b < C::NB; ++b) {
-                    const int row_first = ch * C::RC + (32 * b) / C::HW;
-                    constexpr int kNkLast = C::NK - 1;
-                    const int last_col = (32 * b + 31 < kNkLast) ? 32 * b + 31 : kNkLast;
-                    const int row_last = ch * C::RC + last_col / C::HW;
-                    if (32 * b < C::NK && row_last >= wr_lo && row_first < wr_hi + KS) {     // warp-uniform
-                        uint32_t s[32];
-                        tmem_ld_32x32(s_addr + 32 * b, s);
-                        tmem_ld_wait();
+                for (int t = 0; t < NACT; ++t) {
+                    const int blk = half + 2 * (bi_lo + t);
+                    if (blk < b_hi) tmem_ld_32x16(s_addr + 16 * blk, s[t]);                  // warp-uniform
+                }
+                // validity masks, while the loads are in flight
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const int j = 32 * b + e;
-                            if (j < C::NK) {
-                                const bool ok = ((rm >> (j / C::HW)) & 1u) && ((col_mask >> (j % C::HW)) & 1u);
-                                cmax = fmaxf(cmax, ok ? __uint_as_float(s[e]) : -CUDART_INF_F);
-                            }
+                for (int t = 0; t < NACT; ++t) {
+                    const int blk = half + 2 * (bi_lo + t);
+                    uint32_t m = 0;
+#pragma unroll
+                    for (int u = 0; u < KS; ++u) {
+                        const int r = wr + u - row_off;                    // chunk row of window row u
+                        const int rel = r * C::HW + wc - 16 * blk;         // its first column, relative to the block
+                        const uint32_t seg = (1u << KS) - 1u;
+                        const uint32_t bits = rel >= 0 ? (seg << (rel & 31)) : (seg >> ((-rel) & 31));
+                        if (r >= 0 && r < C::RC && rel > -KS && rel < 16) m |= bits;
+                    }
+                    vmask[t] = (blk < b_hi) ? (m & 0xffffu) : 0u;
+                }
+                tmem_ld_wait();
+                if (tid == 0) NA2D_TR(3, 2, n);
+
+                // masked maximum over this half's blocks, then over both halves
+                float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F;
+#pragma unroll
+                for (int t = 0; t < NACT; ++t) {
+                    if (half + 2 * (bi_lo + t) < b_hi) {
+#pragma unroll
+                        for (int e = 0; e < 16; e += 2) {
+                            m0 = fmaxf(m0, ((vmask[t] >> e) & 1u) ? __uint_as_float(s[t][e]) : -CUDART_INF_F);
+                            m1 = fmaxf(m1, ((vmask[t] >> (e + 1)) & 1u) ? __uint_as_float(s[t][e + 1]) : -CUDART_INF_F);
                         }
                     }
                 }
-                cmax *= kLog2e;
-
-                // The previous chunk's P V is complete (so P may be overwritten and O is stable).
-                mbar_wait(p_free, (n & 1) ^ 1, abort_flag, kErrMmaWait);
+                float cmax = fmaxf(m0, m1);
+                if (tid == 0) NA2D_TR(3, 6, n);
+                x_max[((n & 1) * 2 + half) * 128 + row] = cmax;
+                // This barrier also orders the partner's reads of S before this thread's writes of P,
+                // which land in the same tensor-memory columns.
+                bar_sync(1 + quarter, 64);
+                cmax = fmaxf(cmax, x_max[((n & 1) * 2 + (half ^ 1)) * 128 + row]) * kLog2e;
 
                 // Raise the running maximum only when it would grow by more than the step; a row
                 // whose maximum is still -inf has an all-zero O row and takes the new one freely.
                 const bool grow = cmax > run_max + kRescaleStep;
-                if (ch > 0 && __any_sync(0xffffffffu, grow && run_max != -CUDART_INF_F)) {
-                    const float alpha = grow ? fast_exp2(run_max - cmax) : 1.f;
-                    tc_fence_after();
+                if (C::NCH > 1 && ch > 0) {
+                    mbar_wait(pv_done, (n & 1) ^ 1, abort_flag, kErrMmaWait);     // O holds the previous chunk
+                    if (__any_sync(0xffffffffu, grow && run_max != -CUDART_INF_F)) {
+                        const float alpha = grow ? fast_exp2(run_max - cmax) : 1.f;
+                        tc_fence_after();
 #pragma unroll
-                    for (int piece = 0; piece < D / 32; ++piece) {
-                        uint32_t v[32];
-                        tmem_ld_32x32(o_addr + 32 * piece, v);
-                        tmem_ld_wait();
+                        for (int piece = 0; piece < DH / 16; ++piece) {
+                            uint32_t v[16];
+                            tmem_ld_32x16(o_addr + 16 * piece, v);
+                            tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
-                        tmem_st_32x32(o_addr + 32 * piece, v);
+                            for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+                            tmem_st_32x16(o_addr + 16 * piece, v);
+                        }
+                        run_sum *= alpha;
+                        if (grow) run_max = cmax;
                     }
-                    tmem_st_wait();
-                    run_sum *= alpha;
-                    if (grow) run_max = cmax;
-                } else if (grow) {
-                    run_sum = 0.f;                  // only reachable with run_max == -inf: nothing summed yet
+                }
+                if (grow && cmax > run_max + kRescaleStep) {      // not taken above: run_max was -inf (or first chunk)
+                    run_sum = 0.f;
                     run_max = cmax;
                 }
                 const float safe_max = (run_max == -CUDART_INF_F) ? 0.f : run_max;
+                if (tid == 0) NA2D_TR(3, 3, n);
 
-                // pass 2: P = exp2(s * log2e - max) -> shared memory, row sum
-                float csum = 0.f;
+                // P = exp2(s * log2e - max) as packed 16-bit pairs -> tensor memory (over S), row sum
+                float c0s = 0.f, c1s = 0.f;
 #pragma unroll
-                for (int b = 0; b < C::NB; ++b) {
-                    const int row_first = ch * C::RC + (32 * b) / C::HW;
-                    constexpr int kNkLast = C::NK - 1;
-                    const int last_col = (32 * b + 31 < kNkLast) ? 32 * b + 31 : kNkLast;
-                    const int row_last = ch * C::RC + last_col / C::HW;
-                    uint32_t w[16];
-                    if (32 * b < C::NK && row_last >= wr_lo && row_first < wr_hi + KS) {
-                        uint32_t s[32];
-                        tmem_ld_32x32(s_addr + 32 * b, s);
-                        tmem_ld_wait();
+                for (int t = 0; t < NACT; ++t) {
+                    const int blk = half + 2 * (bi_lo + t);
+                    if (blk < b_hi) {
+                        uint32_t w[8];
 #pragma unroll
-                        for (int e2 = 0; e2 < 16; ++e2) {
-                            float pp[2] = {0.f, 0.f};
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                const int j = 32 * b + 2 * e2 + h;
-                                if (j < C::NK) {
-                                    const bool ok = ((rm >> (j / C::HW)) & 1u) && ((col_mask >> (j % C::HW)) & 1u);
-                                    const float ex = fast_exp2(fmaf(__uint_as_float(s[2 * e2 + h]), kLog2e, -safe_max));
-                                    pp[h] = ok ? ex : 0.f;
-                                    csum += pp[h];
-                                }
-                            }
-                            w[e2] = pack2<DT>(pp[0], pp[1]);
+                        for (int e2 = 0; e2 < 8; ++e2) {
+                            const float e0 = fast_exp2(fmaf(__uint_as_float(s[t][2 * e2]), kLog2e, -safe_max));
+                            const float e1 = fast_exp2(fmaf(__uint_as_float(s[t][2 * e2 + 1]), kLog2e, -safe_max));
+                            const float p0 = ((vmask[t] >> (2 * e2)) & 1u) ? e0 : 0.f;
+                            const float p1 = ((vmask[t] >> (2 * e2 + 1)) & 1u) ? e1 : 0.f;
+                            c0s += p0;
+                            c1s += p1;
+                            w[e2] = pack2<DT>(p0, p1);
                         }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) w[e] = 0u;
+                        tmem_st_32x8(s_addr + 8 * blk, w);
                     }
-                    store_operand_block(smem_u32(sP), C::P_SLAB, tid, b, w);
                 }
-                run_sum += csum;
+                // own blocks outside the range hold zeros
+                {
+                    const uint32_t z[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+                    for (int bi = 0; bi < NBH; ++bi) {
+                        const int blk = half + 2 * bi;
+                        const bool in_range = bi >= bi_lo && bi < bi_lo + NACT && blk < b_hi;
+                        if (!in_range && 16 * blk < C::NKP) tmem_st_32x8(s_addr + 8 * blk, z);
+                    }
+                }
+                run_sum += c0s + c1s;
+                if (tid == 0) NA2D_TR(3, 7, n);
+                tmem_st_wait();
                 tc_fence_before();
-                fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(s_free + sb);
-                    mbar_arrive(p_full);
-                }
+                if (lane == 0) mbar_arrive(p_full);
+                if (tid == 0) NA2D_TR(3, 4, n);
+            };
+
+            for (int ch = 0; ch < C::NCH; ++ch, ++n) {
+                unit(ch);
                 if (pend) epilogue();           // previous tile's output, while this chunk's P V runs
+                if (tid == 0) NA2D_TR(3, 5, n);
             }
+            x_sum[((i & 1) * 2 + half) * 128 + row] = run_sum;
             pend = true;
             pend_tile = (uint32_t)i;
             pend_valid = q_valid;
@@ -373,7 +465,7 @@ int launch_forward(const Na2dGeom& g, int dtype, const void* q, const void* k, c
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return NA2D_ERR_CUDA;
     const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 192, C::SMEM, st>>>(tq, tk, tv, (DT*)o, lse, g, tiles_r, tiles_c, (int)tiles);
+    kern<<<grid, 384, C::SMEM, st>>>(tq, tk, tv, (DT*)o, lse, g, tiles_r, tiles_c, (int)tiles);
     *launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }

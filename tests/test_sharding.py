@@ -1,0 +1,125 @@
+"""CPU tests (gloo, world size 2 and 3) of the multi-GPU host logic: unit partition, row-band
+plan, K/V halo exchange and dK/dV halo reduction.  The arithmetic of each band is supplied by the
+CPU oracle, so what is under test is the exchange itself: the bands must reassemble to the
+whole-image result."""
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from e_natten_b200 import sharding
+from oracle import na2d_oracle as orc
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_partition_units_covers_everything_once():
+    for n in (1, 7, 16, 128, 256):
+        for world in (1, 2, 3, 4, 8):
+            spans = [sharding.partition_units(n, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and sum(c for _, c in spans) == n
+            for (a, ca), (b, _) in zip(spans, spans[1:]):
+                assert a + ca == b
+            assert max(c for _, c in spans) - min(c for _, c in spans) <= 1
+
+
+def test_row_shard_plan_matches_window_union():
+    for H, world, ks in ((1024, 8, 13), (1024, 2, 13), (48, 3, 5), (40, 2, 7), (39, 3, 13)):
+        covered = 0
+        for r in range(world):
+            sh = sharding.plan_row_shard(H, world, r, ks)
+            assert sh.row0 == covered
+            covered += sh.R
+            lo = min(orc.window_start(x, H, ks) for x in range(sh.row0, sh.row0 + sh.R))
+            hi = max(orc.window_start(x, H, ks) + ks for x in range(sh.row0, sh.row0 + sh.R))
+            assert (sh.kv_row0, sh.kv_row0 + sh.Hkv) == (lo, hi)
+            assert 0 <= sh.top <= ks // 2 and 0 <= sh.bot <= ks // 2
+            assert (sh.top == 0) == (r == 0) and (sh.bot == 0) == (r == world - 1)
+        assert covered == H
+    with pytest.raises(ValueError):
+        sharding.plan_row_shard(20, 4, 0, 7)          # bands of 5 rows < kernel size
+
+
+def _oracle_forward(q, k_ext, v_ext, ks, rows):
+    o, lse = orc.natten2d_fwd(q, k_ext, v_ext, ks, rows=(rows.q_row0, rows.kv_row0, rows.H_global))
+    return o.to(q.dtype), lse.float()
+
+
+def _oracle_backward(q, k_ext, v_ext, o, lse, d_o, ks, rows):
+    dq, dk, dv = orc.natten2d_bwd(q, k_ext, v_ext, d_o, ks, rows=(rows.q_row0, rows.kv_row0, rows.H_global))
+    return dq.to(q.dtype), dk.to(q.dtype), dv.to(q.dtype)
+
+
+def _worker(rank, world, port, H, W, ks, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        q, k, v, d_o = orc.round_inputs((1, 2, H, W, 3), torch.float64, 17)
+        sh = sharding.plan_row_shard(H, world, rank, ks)
+        band = slice(sh.row0, sh.row0 + sh.R)
+        ql, kl, vl = (t[:, :, band].clone().requires_grad_() for t in (q, k, v))
+        o = sharding.natten2d_row_sharded(ql, kl, vl, ks, H, forward_fn=_oracle_forward, backward_fn=_oracle_backward)
+        o.backward(d_o[:, :, band])
+        ro, _, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks)
+        err = max((o.detach() - ro[:, :, band]).abs().max().item(),
+                  (ql.grad - rdq[:, :, band]).abs().max().item(),
+                  (kl.grad - rdk[:, :, band]).abs().max().item(),
+                  (vl.grad - rdv[:, :, band]).abs().max().item())
+        errs = [None] * world
+        dist.all_gather_object(errs, err)
+        if rank == 0:
+            result.put(max(errs))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,H,W,ks", [(2, 20, 9, 5), (3, 40, 14, 13), (2, 26, 14, 13), (3, 24, 7, 7)])
+def test_row_sharded_bands_equal_whole_image(world, H, W, ks):
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, H, W, ks, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert result.get(timeout=5) < 1e-12
+
+
+def _lonely_worker(rank, world, port, result):
+    """Rank 1 leaves before the exchange; rank 0 must get an error from its bounded wait, not hang."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    if rank == 1:
+        os._exit(0)                                   # a rank that never takes part in the exchange
+    q, k, v, _ = orc.round_inputs((1, 1, 20, 8, 2), torch.float64, 3)
+    sh = sharding.plan_row_shard(20, world, rank, 5)
+    band = slice(sh.row0, sh.row0 + sh.R)
+    try:
+        sharding.exchange_kv_halo(k[:, :, band].contiguous(), v[:, :, band].contiguous(), sh)
+        result.put("no error")
+    except Exception as exc:                          # noqa: BLE001 - any error from the transport is the point
+        result.put("error: " + type(exc).__name__)
+    os._exit(0)
+
+
+def test_missing_neighbour_is_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_lonely_worker, args=(r, 2, port, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+    assert all(not p.is_alive() for p in procs)
+    assert result.get(timeout=5).startswith("error")
