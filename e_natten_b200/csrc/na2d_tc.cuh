@@ -164,6 +164,13 @@ inline int make_map(CUtensorMap* map, const void* base, int dtype, long long BN,
     return r == CUDA_SUCCESS ? NA2D_OK : NA2D_ERR_CUDA;
 }
 
+// Register re-balancing of the 384-thread kernels (launched with 168 registers per thread): the
+// four warps of the data-movement group shrink to kRegsDonor, the eight softmax warps grow to
+// kRegsSoftmax.  setmaxnreg.inc blocks until the registers it asks for have been given up, so
+// what the eight warps take must not exceed what the four release.
+constexpr int kRegsLaunch = 168, kRegsDonor = 64, kRegsSoftmax = 216;
+static_assert((kRegsSoftmax - kRegsLaunch) * 8 <= (kRegsLaunch - kRegsDonor) * 4, "setmaxnreg.inc would wait for ever");
+
 constexpr int kSmemLimit = 232448;     // dynamic shared memory a CTA can opt in to on sm_100
 
 // Number of SMs of `device` (persistent kernels launch one CTA per SM), cached.
@@ -208,6 +215,7 @@ inline bool supported(int dtype, int C, int ks) {
 
 #include "na2d_tc_fwd.cuh"
 #include "na2d_tc_bwd.cuh"
+#include "na2d_tc_dkdv.cuh"
 
 namespace na2d_tc {
 

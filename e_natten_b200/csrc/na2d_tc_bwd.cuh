@@ -287,306 +287,6 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     }
 }
 
-// ------------------------------------------------------------------------------------ dK, dV
-template <int D, int KS, bool SPLIT>
-struct DkvCfg : Cfg<D, KS, 128> {
-    using B = Cfg<D, KS, 128>;
-    // names of the base read as "queries per chunk" here: NK = queries in a chunk, NKP padded
-    static constexpr int TMEM_ST = 0, TMEM_DPT = 128, TMEM_DV = 256, TMEM_DK = 384;
-    static constexpr int N_OPERANDS = SPLIT ? 3 : 2;       // P^T, dS^T (, residual of dS^T)
-    static constexpr int SMEM = 2 * B::Q_BYTES /*K, V tile*/ + 2 * B::KV_BYTES /*Q, dO chunk*/ +
-                                N_OPERANDS * B::P_BYTES + 2 * 128 * 4 /*lse, delta*/ + 64 + 1024;
-    static_assert(SMEM <= kSmemLimit, "dK/dV kernel shared memory");
-};
-
-template <typename DT, int D, int KS>
-__global__ void __launch_bounds__(128, 1)
-dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-            const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-            const float* __restrict__ lse, const float* __restrict__ delta,
-            DT* __restrict__ d_k, DT* __restrict__ d_v, const Na2dGeom g, const int tiles_r, const int tiles_c) {
-    constexpr bool SPLIT = IsBf16<DT>::value;         // bf16: dS^T goes to the MMA as head + residual
-    using C = DkvCfg<D, KS, SPLIT>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sK = smem;                         // key tile   [128 x D]
-    uint8_t* sV = sK + C::Q_BYTES;              // value tile [128 x D]
-    uint8_t* sQ = sV + C::Q_BYTES;              // query chunk [NKP x D]
-    uint8_t* sDO = sQ + C::KV_BYTES;            // dO chunk    [NKP x D]
-    uint8_t* sPT = sDO + C::KV_BYTES;           // P^T   [128 x NKP]
-    uint8_t* sDST = sPT + C::P_BYTES;           // dS^T  [128 x NKP]
-    uint8_t* sRES = sDST + C::P_BYTES;          // residual half of dS^T (bf16 path only)
-    float* s_lse = reinterpret_cast<float*>(sPT + C::N_OPERANDS * C::P_BYTES);   // lse * log2(e) of the chunk's queries
-    float* s_delta = s_lse + 128;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 128);
-    uint64_t* bar_load = bars + 0;
-    uint64_t* bar_s = bars + 1;
-    uint64_t* bar_o = bars + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-
-    const int tid = threadIdx.x, warp = tid >> 5;
-    int t = blockIdx.x;
-    const int tc = t % tiles_c;
-    t /= tiles_c;
-    const int tr = t % tiles_r;
-    const int bn = t / tiles_r;
-    const int kr0 = tr * TH, kc0 = tc * TW;                       // key-band coordinates of the tile
-    // query box: union of the inverse neighbourhoods of the tile's keys, clipped to the query band
-    const int kg_first = g.kv_row0 + kr0;
-    const int kg_last = g.kv_row0 + min(kr0 + TH, g.Hkv) - 1;
-    const int qb_r0 = max(na2d_bws(kg_first, KS), g.q_row0);                        // global row
-    const int qb_r1 = min(na2d_bwe(kg_last, g.Hg, KS), g.q_row0 + g.Hq);
-    const int n_rows = max(qb_r1 - qb_r0, 0);
-    // The box is walked in chunks of RC rows x HW columns.  Inside the image one column chunk is
-    // enough; where the inverse ranges are stretched by the clamping at both borders (first key
-    // column below ks and last one within ks of the right edge) the box is wider than HW and takes two.
-    const int qb_c0 = na2d_bws(kc0, KS);
-    const int n_cols = na2d_bwe(min(kc0 + TW, g.W) - 1, g.W, KS) - qb_c0;
-    const int n_cc = (n_cols + C::HW - 1) / C::HW;
-    const int n_ch = ((n_rows + C::RC - 1) / C::RC) * n_cc;
-    const int q_local_r0 = qb_r0 - g.q_row0;                                        // query-band row
-
-    if (tid == 0) {
-        *abort_flag = 0;
-        mbar_init(bar_load, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
-        mbar_fence_init();
-        tma_prefetch_desc(&tm_k);
-        tma_prefetch_desc(&tm_v);
-        tma_prefetch_desc(&tm_q);
-        tma_prefetch_desc(&tm_do);
-    }
-    if (warp == 0) {
-        __syncwarp();
-        tmem_alloc(tmem_slot, C::TMEM_COLS);
-        tmem_relinquish();
-    }
-    // Rows [NK, NKP) of the query and dO chunks are contraction rows of the two output MMAs and
-    // are never written by TMA: zero them once.
-    if constexpr (C::NKP > C::NK) {
-        constexpr int pad16 = (C::NKP - C::NK) * C::ROWB / 16;
-        for (int i = tid; i < 2 * C::NS * pad16; i += 128) {
-            const int which = i / pad16, off = i - which * pad16;
-            uint8_t* base = (which < C::NS ? sQ + which * C::KV_SLAB : sDO + (which - C::NS) * C::KV_SLAB);
-            st_shared_v4(smem_u32(base + C::NK * C::ROWB + off * 16), 0u, 0u, 0u, 0u);
-        }
-        fence_proxy_async();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-
-    // this thread's key and the queries that can see it, as bit masks over the query box
-    const int kr_raw = kr0 + (tid / TW), kc_raw = kc0 + (tid % TW);
-    const bool k_valid = kr_raw < g.Hkv && kc_raw < g.W;
-    const int kr = min(kr_raw, g.Hkv - 1), kc = min(kc_raw, g.W - 1);
-    const size_t ki = (static_cast<size_t>(bn) * g.Hkv + kr) * g.W + kc;
-    const int kg = g.kv_row0 + kr;
-    const int row_lo = max(na2d_bws(kg, KS), g.q_row0) - qb_r0;                     // box rows [row_lo, row_hi)
-    const int row_hi = min(na2d_bwe(kg, g.Hg, KS), g.q_row0 + g.Hq) - qb_r0;
-    const int col_lo = na2d_bws(kc, KS) - qb_c0;                                    // box cols [col_lo, col_hi)
-    const int col_hi = na2d_bwe(kc, g.W, KS) - qb_c0;
-    auto range_mask = [](int lo, int hi) -> uint32_t {
-        lo = max(lo, 0);
-        hi = min(hi, 32);
-        if (hi <= lo) return 0u;
-        const uint32_t upto_hi = hi >= 32 ? 0xffffffffu : ((1u << hi) - 1u);
-        return upto_hi & ~((1u << lo) - 1u);
-    };
-    auto range_mask64 = [](int lo, int hi) -> uint64_t {      // the query box can be up to 40 rows tall
-        lo = max(lo, 0);
-        hi = min(hi, 64);
-        if (hi <= lo) return 0ull;
-        const uint64_t upto_hi = hi >= 64 ? ~0ull : ((1ull << hi) - 1ull);
-        return upto_hi & ~((1ull << lo) - 1ull);
-    };
-    const uint64_t row_mask = range_mask64(row_lo, row_hi);
-    const uint64_t col_mask64 = range_mask64(col_lo, col_hi);
-    const int wrow_lo = __shfl_sync(0xffffffffu, row_lo, 0);     // the warp's keys are seen from box rows
-    const int wrow_hi = __shfl_sync(0xffffffffu, row_hi, 31);    //   [wrow_lo, wrow_hi)
-
-    constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
-    constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
-    uint32_t ph_load = 0, ph_s = 0, ph_o = 0;
-
-    for (int ch = 0; ch < n_ch; ++ch) {
-        const int rc = ch / n_cc, cc = ch - rc * n_cc;          // row chunk, column chunk
-        if (tid == 0) {
-            if (ch > 0) {                       // the previous chunk's output MMAs still read sQ / sDO
-                mbar_wait(bar_o, ph_o, abort_flag, kErrMmaWait);
-                tc_fence_after();
-            }
-            const uint32_t q_bytes = 2u * C::NS * C::NK * C::ROWB;
-            mbar_expect_tx(bar_load, q_bytes + (ch == 0 ? 2u * C::Q_BYTES : 0u));
-#pragma unroll
-            for (int s = 0; s < C::NS; ++s) {
-                if (ch == 0) {
-                    tma_load_4d(sK + s * C::Q_SLAB, &tm_k, bar_load, s * 64, kc0, kr0, bn);
-                    tma_load_4d(sV + s * C::Q_SLAB, &tm_v, bar_load, s * 64, kc0, kr0, bn);
-                }
-                tma_load_4d(sQ + s * C::KV_SLAB, &tm_q, bar_load, s * 64, qb_c0 + cc * C::HW, q_local_r0 + rc * C::RC, bn);
-                tma_load_4d(sDO + s * C::KV_SLAB, &tm_do, bar_load, s * 64, qb_c0 + cc * C::HW, q_local_r0 + rc * C::RC, bn);
-            }
-            mbar_wait(bar_load, ph_load, abort_flag, kErrLoadWait);
-            ph_load ^= 1u;
-            tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                const int slab = (kk * 16) / C::SLAB_C, in_slab = (kk * 16) % C::SLAB_C;
-                const uint64_t ak = smem_desc(smem_u32(sK + slab * C::Q_SLAB) + in_slab * 2, 16, C::ATOM, C::SWZ);
-                const uint64_t bq = smem_desc(smem_u32(sQ + slab * C::KV_SLAB) + in_slab * 2, 16, C::ATOM, C::SWZ);
-                umma_ss(tmem_base + C::TMEM_ST, ak, bq, idesc_s, kk > 0);
-            }
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                const int slab = (kk * 16) / C::SLAB_C, in_slab = (kk * 16) % C::SLAB_C;
-                const uint64_t av = smem_desc(smem_u32(sV + slab * C::Q_SLAB) + in_slab * 2, 16, C::ATOM, C::SWZ);
-                const uint64_t bg = smem_desc(smem_u32(sDO + slab * C::KV_SLAB) + in_slab * 2, 16, C::ATOM, C::SWZ);
-                umma_ss(tmem_base + C::TMEM_DPT, av, bg, idesc_s, kk > 0);
-            }
-            umma_commit(bar_s);
-        }
-        __syncwarp();
-        if (ch > 0 && tid != 0) {               // keep every thread's view of bar_o in step
-            mbar_wait(bar_o, ph_o, abort_flag, kErrMmaWait);
-        }
-        if (ch > 0) ph_o ^= 1u;
-
-        // lse and delta of this chunk's queries (one per thread), zero outside the query band
-        {
-            float l2 = 0.f, dl = 0.f;
-            if (tid < C::NK) {
-                const int br = rc * C::RC + tid / C::HW, bc = tid % C::HW;      // box row / column
-                const int qc = qb_c0 + cc * C::HW + bc;
-                if (br < n_rows && qc < g.W) {
-                    const size_t qi = (static_cast<size_t>(bn) * g.Hq + (q_local_r0 + br)) * g.W + qc;
-                    l2 = lse[qi] * kLog2e;
-                    dl = delta[qi];
-                }
-            }
-            s_lse[tid] = l2;
-            s_delta[tid] = dl;
-        }
-        __syncthreads();
-        mbar_wait(bar_s, ph_s, abort_flag, kErrMmaWait);
-        ph_s ^= 1u;
-        tc_fence_after();
-
-        const uint32_t rm = static_cast<uint32_t>(row_mask >> (rc * C::RC));
-        const uint32_t col_mask = static_cast<uint32_t>(col_mask64 >> (cc * C::HW));
-#pragma unroll
-        for (int b = 0; b < C::NB; ++b) {
-            const int row_first = rc * C::RC + (32 * b) / C::HW;
-            const int last_col = (32 * b + 31 < C::NK - 1) ? 32 * b + 31 : C::NK - 1;
-            const int row_last = rc * C::RC + last_col / C::HW;
-            uint32_t wp[16], wd[16], wr2[16];
-            if (32 * b < C::NK && row_last >= wrow_lo && row_first < wrow_hi) {      // warp-uniform
-                uint32_t s[32], dp[32];
-                tmem_ld_32x32(tmem_lane + C::TMEM_ST + 32 * b, s);
-                tmem_ld_32x32(tmem_lane + C::TMEM_DPT + 32 * b, dp);
-                tmem_ld_wait();
-                float p[32], ds[32];
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int j = 32 * b + e;
-                    p[e] = 0.f;
-                    ds[e] = 0.f;
-                    if (j < C::NK) {
-                        const bool ok = ((rm >> (j / C::HW)) & 1u) && ((col_mask >> (j % C::HW)) & 1u);
-                        const float pe = fast_exp2(fmaf(__uint_as_float(s[e]), kLog2e, -s_lse[j]));
-                        p[e] = ok ? pe : 0.f;
-                        ds[e] = ok ? pe * (__uint_as_float(dp[e]) - s_delta[j]) : 0.f;
-                    }
-                }
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    wp[e] = pack2<DT>(p[2 * e], p[2 * e + 1]);
-                    wd[e] = pack2<DT>(ds[2 * e], ds[2 * e + 1]);
-                    wr2[e] = SPLIT ? pack2_residual_bf16(ds[2 * e], ds[2 * e + 1], wd[e]) : 0u;
-                }
-            } else {
-#pragma unroll
-                for (int e = 0; e < 16; ++e) { wp[e] = 0u; wd[e] = 0u; wr2[e] = 0u; }
-            }
-            store_operand_block(smem_u32(sPT), C::P_SLAB, tid, b, wp);
-            store_operand_block(smem_u32(sDST), C::P_SLAB, tid, b, wd);
-            if (SPLIT) store_operand_block(smem_u32(sRES), C::P_SLAB, tid, b, wr2);
-        }
-        fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < C::NKP / 16; ++kk) {
-                const uint64_t ap = smem_desc(smem_u32(sPT + (kk >> 2) * C::P_SLAB) + (kk & 3) * 32, 16, 1024, 2u);
-                const uint64_t bg = smem_desc(smem_u32(sDO) + kk * 16 * C::ROWB, C::KV_SLAB, C::ATOM, C::SWZ);
-                umma_ss(tmem_base + C::TMEM_DV, ap, bg, idesc_o, (ch > 0) || (kk > 0));
-            }
-#pragma unroll
-            for (int kk = 0; kk < C::NKP / 16; ++kk) {
-                const uint64_t ad = smem_desc(smem_u32(sDST + (kk >> 2) * C::P_SLAB) + (kk & 3) * 32, 16, 1024, 2u);
-                const uint64_t bq = smem_desc(smem_u32(sQ) + kk * 16 * C::ROWB, C::KV_SLAB, C::ATOM, C::SWZ);
-                umma_ss(tmem_base + C::TMEM_DK, ad, bq, idesc_o, (ch > 0) || (kk > 0));
-            }
-            if (SPLIT) {
-#pragma unroll
-                for (int kk = 0; kk < C::NKP / 16; ++kk) {
-                    const uint64_t ad = smem_desc(smem_u32(sRES + (kk >> 2) * C::P_SLAB) + (kk & 3) * 32, 16, 1024, 2u);
-                    const uint64_t bq = smem_desc(smem_u32(sQ) + kk * 16 * C::ROWB, C::KV_SLAB, C::ATOM, C::SWZ);
-                    umma_ss(tmem_base + C::TMEM_DK, ad, bq, idesc_o, 1u);
-                }
-            }
-            umma_commit(bar_o);
-        }
-        __syncwarp();
-    }
-    if (n_ch > 0) {
-        mbar_wait(bar_o, ph_o, abort_flag, kErrMmaWait);
-        tc_fence_after();
-    }
-
-    // ---- epilogue: dV and dK rows of this thread's key -------------------------------------------------
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-        DT* row = (which == 0 ? d_v : d_k) + ki * D;
-        const int col0 = which == 0 ? C::TMEM_DV : C::TMEM_DK;
-#pragma unroll
-        for (int piece = 0; piece < D / 32; ++piece) {
-            uint32_t v[32];
-            if (n_ch > 0) {
-                tmem_ld_32x32(tmem_lane + col0 + 32 * piece, v);
-                tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int e = 0; e < 32; ++e) v[e] = 0u;      // no local query sees this tile
-            }
-            if (k_valid) {
-#pragma unroll
-                for (int gI = 0; gI < 4; ++gI) {
-                    uint4 pk;
-                    pk.x = pack2<DT>(__uint_as_float(v[8 * gI + 0]), __uint_as_float(v[8 * gI + 1]));
-                    pk.y = pack2<DT>(__uint_as_float(v[8 * gI + 2]), __uint_as_float(v[8 * gI + 3]));
-                    pk.z = pack2<DT>(__uint_as_float(v[8 * gI + 4]), __uint_as_float(v[8 * gI + 5]));
-                    pk.w = pack2<DT>(__uint_as_float(v[8 * gI + 6]), __uint_as_float(v[8 * gI + 7]));
-                    *reinterpret_cast<uint4*>(row + 32 * piece + 8 * gI) = pk;
-                }
-            }
-        }
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) {
-        tc_fence_after();
-        tmem_dealloc(tmem_base, C::TMEM_COLS);
-    }
-}
-
 // ------------------------------------------------------------------------------------ launchers
 template <typename DT, int D, int KS>
 int launch_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
@@ -609,42 +309,12 @@ int launch_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const 
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }
 
-template <typename DT, int D, int KS>
-int launch_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-                const void* d_o, const float* delta, void* d_k, void* d_v, cudaStream_t st, int* launched) {
-    using C = DkvCfg<D, KS, IsBf16<DT>::value>;
-    CUtensorMap tk, tv, tq, tg;
-    int rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, C::HW, C::RC);
-    if (rc == NA2D_OK) rc = make_map(&tg, d_o, dtype, g.BN, g.Hq, g.W, D, C::HW, C::RC);
-    if (rc != NA2D_OK) return rc;
-    const int tiles_r = (g.Hkv + TH - 1) / TH, tiles_c = (g.W + TW - 1) / TW;
-    const long long tiles = (long long)g.BN * tiles_r * tiles_c;
-    if (tiles > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
-    auto kern = dkdv_kernel<DT, D, KS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-        return NA2D_ERR_CUDA;
-    kern<<<(unsigned)tiles, 128, C::SMEM, st>>>(tk, tv, tq, tg, lse, delta, (DT*)d_k, (DT*)d_v, g, tiles_r, tiles_c);
-    *launched += 1;
-    return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
-}
-
 inline int backward_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const void* /*o*/,
                        const float* lse, const void* d_o, void* d_q, float* delta, int, cudaStream_t st, int* launched) {
     if (dtype == NA2D_BF16) {
         NA2D_TC_DISPATCH_D(launch_dq, __nv_bfloat16, g, dtype, q, k, v, lse, d_o, d_q, delta, st, launched)
     } else {
         NA2D_TC_DISPATCH_D(launch_dq, __half, g, dtype, q, k, v, lse, d_o, d_q, delta, st, launched)
-    }
-}
-
-inline int backward_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-                         const void* d_o, const float* delta, void* d_k, void* d_v, int, cudaStream_t st, int* launched) {
-    if (dtype == NA2D_BF16) {
-        NA2D_TC_DISPATCH_D(launch_dkdv, __nv_bfloat16, g, dtype, q, k, v, lse, d_o, delta, d_k, d_v, st, launched)
-    } else {
-        NA2D_TC_DISPATCH_D(launch_dkdv, __half, g, dtype, q, k, v, lse, d_o, delta, d_k, d_v, st, launched)
     }
 }
 

@@ -50,9 +50,17 @@ struct FwdCfg : Cfg<D, KS, 256> {
     static constexpr int K_BYTES = B::NS * K_SLAB;
     static constexpr int V_BYTES = B::KV_BYTES;
     static constexpr int XCHG_BYTES = 4 * 2 * 128 * 4;                  // row max [2][2][128], row sum [2][2][128]
-    static constexpr int FIXED = 2 * B::Q_BYTES + XCHG_BYTES + 256 /*barriers*/ + 1024 /*alignment*/;
-    static constexpr int NSTAGE = (FIXED + 2 * (K_BYTES + V_BYTES) <= kSmemLimit) ? 2 : 1;   // K and V ring depth
-    static constexpr int SMEM = FIXED + NSTAGE * (K_BYTES + V_BYTES);
+    static constexpr int FIXED = XCHG_BYTES + 256 /*barriers*/ + 1024 /*alignment*/;
+    // Ring depths, given out in the order that pays most: a second V slot first (a V slot is only
+    // free after the chunk's last MMA, so its refill is what the next tile would wait for), then a
+    // second K slot, then a second Q tile.
+    static constexpr bool fits(int nq, int nk, int nv) {
+        return FIXED + nq * B::Q_BYTES + nk * K_BYTES + nv * V_BYTES <= kSmemLimit;
+    }
+    static constexpr int NSTV = fits(1, 1, 2) ? 2 : 1;
+    static constexpr int NSTK = fits(1, 2, NSTV) ? 2 : 1;
+    static constexpr int NQ = fits(2, NSTK, NSTV) ? 2 : 1;
+    static constexpr int SMEM = FIXED + NQ * B::Q_BYTES + NSTK * K_BYTES + NSTV * V_BYTES;
     static constexpr int NB16 = (B::NKP + 15) / 16;                     // 16-column blocks of S
     static constexpr int TMEM_S = 0, TMEM_O0 = 256, TMEM_OSTRIDE = 128; // S / P at 0, O[2] at 256 / 384
     static_assert(SMEM <= kSmemLimit, "forward kernel shared memory");
@@ -65,13 +73,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
            const __grid_constant__ CUtensorMap tm_v, DT* __restrict__ o, float* __restrict__ lse,
            const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
     using C = FwdCfg<D, KS>;
-    constexpr int NST = C::NSTAGE;
+    constexpr int NSTK = C::NSTK, NSTV = C::NSTV, NQ = C::NQ;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;                                   // 2 x Q tile
-    uint8_t* sK = sQ + 2 * C::Q_BYTES;                    // NST x K chunk
-    uint8_t* sV = sK + NST * C::K_BYTES;                  // NST x V chunk
-    float* x_max = reinterpret_cast<float*>(sV + NST * C::V_BYTES);   // [unit parity][half][row]
+    uint8_t* sQ = smem;                                   // NQ x Q tile
+    uint8_t* sK = sQ + NQ * C::Q_BYTES;                   // NSTK x K chunk
+    uint8_t* sV = sK + NSTK * C::K_BYTES;                 // NSTV x V chunk
+    float* x_max = reinterpret_cast<float*>(sV + NSTV * C::V_BYTES);  // [unit parity][half][row]
     float* x_sum = x_max + 2 * 2 * 128;                               // [tile parity][half][row]
     uint64_t* bars = reinterpret_cast<uint64_t*>(x_sum + 2 * 2 * 128);
     uint64_t* q_full = bars;                 // [2]   TMA -> MMA
@@ -120,7 +128,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // V rows [NK, NKP) of every stage are contraction rows of P V that TMA never writes.
     if constexpr (C::NKP > C::NK) {
         constexpr int pad16 = (C::NKP - C::NK) * C::ROWB / 16;
-        for (int i = tid; i < NST * C::NS * pad16; i += 384) {
+        for (int i = tid; i < NSTV * C::NS * pad16; i += 384) {
             const int which = i / pad16, off = i - which * pad16;
             const int st = which / C::NS, slab = which % C::NS;
             uint8_t* base = sV + st * C::V_BYTES + slab * C::KV_SLAB;
@@ -144,7 +152,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
     if (warp == 8) {
         // ------------------------------------------------------------------ producer
-        reg_dec<64>();
+        reg_dec<kRegsDonor>();
         if (lane == 0) {
             uint32_t n = 0;
             for (int i = 0; i < n_my; ++i) {
@@ -152,28 +160,28 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 decode(i, bn, r0, c0);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
-                const int qb = i & 1;
-                mbar_wait(q_empty + qb, ((i >> 1) & 1) ^ 1, abort_flag, kErrLoadWait);
+                const int qb = i % NQ;
+                mbar_wait(q_empty + qb, ((i / NQ) & 1) ^ 1, abort_flag, kErrLoadWait);
                 mbar_expect_tx(q_full + qb, C::Q_BYTES);
 #pragma unroll
                 for (int s = 0; s < C::NS; ++s)
                     tma_load_4d(sQ + qb * C::Q_BYTES + s * C::Q_SLAB, &tm_q, q_full + qb, s * 64, c0, r0, bn);
                 for (int c = 0; c < C::NCH; ++c, ++n) {
-                    const uint32_t st = n % NST, ph = ((n / NST) & 1) ^ 1;
+                    const uint32_t sk = n % NSTK, sv = n % NSTV;
                     NA2D_TR(1, 0, n);
-                    mbar_wait(k_empty + st, ph, abort_flag, kErrLoadWait);
+                    mbar_wait(k_empty + sk, ((n / NSTK) & 1) ^ 1, abort_flag, kErrLoadWait);
                     NA2D_TR(1, 1, n);
-                    mbar_expect_tx(k_full + st, (uint32_t)C::NS * C::NK * C::ROWB);
+                    mbar_expect_tx(k_full + sk, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
-                        tma_load_4d(sK + st * C::K_BYTES + s * C::K_SLAB, &tm_k, k_full + st, s * 64, box_c0,
+                        tma_load_4d(sK + sk * C::K_BYTES + s * C::K_SLAB, &tm_k, k_full + sk, s * 64, box_c0,
                                     box_r0 + c * C::RC, bn);
-                    mbar_wait(v_empty + st, ph, abort_flag, kErrLoadWait);
+                    mbar_wait(v_empty + sv, ((n / NSTV) & 1) ^ 1, abort_flag, kErrLoadWait);
                     NA2D_TR(1, 2, n);
-                    mbar_expect_tx(v_full + st, (uint32_t)C::NS * C::NK * C::ROWB);
+                    mbar_expect_tx(v_full + sv, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
-                        tma_load_4d(sV + st * C::V_BYTES + s * C::KV_SLAB, &tm_v, v_full + st, s * 64, box_c0,
+                        tma_load_4d(sV + sv * C::V_BYTES + s * C::KV_SLAB, &tm_v, v_full + sv, s * 64, box_c0,
                                     box_r0 + c * C::RC, bn);
                 }
             }
@@ -181,20 +189,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
         // (the whole warp walks the loop so that addresses stay warp-uniform; one lane issues)
-        reg_dec<64>();
+        reg_dec<kRegsDonor>();
         const bool leader = lane == 0;
         constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
         constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
         constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
         for (uint32_t n = 0; n < total_units; ++n) {
-            const uint32_t i = n / C::NCH, c = n % C::NCH, st = n % NST, ph = (n / NST) & 1, ob = i & 1;
+            const uint32_t i = n / C::NCH, c = n % C::NCH, sk = n % NSTK, sv = n % NSTV, qb = i % NQ, ob = i & 1;
             if (lane == 0) NA2D_TR(2, 0, n);
-            if (c == 0) mbar_wait(q_full + (i & 1), (i >> 1) & 1, abort_flag, kErrLoadWait);
-            mbar_wait(k_full + st, ph, abort_flag, kErrLoadWait);
+            if (c == 0) mbar_wait(q_full + qb, (i / NQ) & 1, abort_flag, kErrLoadWait);
+            mbar_wait(k_full + sk, (n / NSTK) & 1, abort_flag, kErrLoadWait);
             if (lane == 0) NA2D_TR(2, 1, n);
             tc_fence_after();
-            const uint32_t q_lo = smem_desc_lo(smem_u32(sQ + (i & 1) * C::Q_BYTES), 16);
-            const uint32_t k_lo = smem_desc_lo(smem_u32(sK + st * C::K_BYTES), 16);
+            const uint32_t q_lo = smem_desc_lo(smem_u32(sQ + qb * C::Q_BYTES), 16);
+            const uint32_t k_lo = smem_desc_lo(smem_u32(sK + sk * C::K_BYTES), 16);
             if (leader) {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -204,24 +212,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                             desc64(hi, k_lo + ((slab * C::K_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
                 }
                 umma_commit(s_full);
-                umma_commit(k_empty + st);
-                if (c == C::NCH - 1) umma_commit(q_empty + (i & 1));      // the tile's Q buffer is free
+                umma_commit(k_empty + sk);
+                if (c == C::NCH - 1) umma_commit(q_empty + qb);           // the tile's Q buffer is free
             }
             __syncwarp();
             if (lane == 0) NA2D_TR(2, 2, n);
-            mbar_wait(v_full + st, ph, abort_flag, kErrLoadWait);
+            mbar_wait(v_full + sv, (n / NSTV) & 1, abort_flag, kErrLoadWait);
             mbar_wait(p_full, n & 1, abort_flag, kErrMmaWait);
             if (lane == 0) NA2D_TR(2, 3, n);
             if (c == 0) mbar_wait(o_free + ob, ((i >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
             tc_fence_after();
-            const uint32_t v_lo = smem_desc_lo(smem_u32(sV + st * C::V_BYTES), C::KV_SLAB);
+            const uint32_t v_lo = smem_desc_lo(smem_u32(sV + sv * C::V_BYTES), C::KV_SLAB);
             if (leader) {
 #pragma unroll
                 for (int kk = 0; kk < C::NKP / 16; ++kk) {
                     umma_ts(tmem_base + C::TMEM_O0 + ob * C::TMEM_OSTRIDE, tmem_base + C::TMEM_S + 8 * kk,
                             desc64(hi, v_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, (c > 0) || (kk > 0));
                 }
-                umma_commit(v_empty + st);
+                umma_commit(v_empty + sv);
                 umma_commit(pv_done);
                 if (c == C::NCH - 1) umma_commit(o_full + ob);
             }
@@ -229,10 +237,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             if (lane == 0) NA2D_TR(2, 4, n);
         }
     } else if (warp >= 10) {
-        reg_dec<64>();                 // spare warps of the data-movement group
+        reg_dec<kRegsDonor>();                 // spare warps of the data-movement group
     } else {
         // ------------------------------------------------------------------ softmax warps
-        reg_inc<216>();
+        reg_inc<kRegsSoftmax>();
         const int quarter = warp & 3, half = warp >> 2;
         const int row = quarter * 32 + lane;                 // query of the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
