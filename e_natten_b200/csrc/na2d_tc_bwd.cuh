@@ -1,77 +1,88 @@
-// tcgen05 backward kernels: dQ (+ row delta) and dK/dV.  Included by na2d_tc.cuh.
+// Persistent, warp-specialised tcgen05 dQ kernel (also produces the row delta).  Included by
+// na2d_tc.cuh.
 //
-// Both recompute P from the saved row log-sum-exp: p = exp(s - lse).  The row delta is formed as
-// delta = sum_j p_j * dp_j (dp_j = dO . v_j), which equals dO . o exactly and does not depend on
-// how o was rounded when it was stored; the dQ kernel writes it to scratch for the dK/dV kernel.
-//
-// dQ kernel (one CTA per TH x TW query tile, rows = queries):
-//   phase A, per key chunk:  S = Q K^T, dP = dO V^T  ->  delta += sum_j p dp      (registers)
-//   phase B, per key chunk:  dS = p (dP - delta)  ->  shared  ->  dQ += dS K      (tensor memory)
-//   With a single chunk (ks <= 5) S and dP stay in tensor memory between the phases and dQ reuses
-//   the S columns; with several chunks phase B reloads the chunk and repeats the two MMAs.
-//
-// dK/dV kernel (one CTA per TH x TW key tile, rows = keys): the queries that can see the tile are
-//   the union of the keys' inverse neighbourhoods, a box of query pixels walked in chunks:
-//   S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T -> shared  ->  dV += P^T dO, dK += dS^T Q.
+// One CTA per SM walks query tiles (TH x TW queries, row r of every MMA = query r =
+// tensor-memory lane r).  The tile's halo box of keys is taken in chunks of whole box rows.
+//     S = Q K_c^T,  dP = dO V_c^T                          (tensor memory, fp32)
+//     p = exp(S - lse),  delta = sum_j p dP                (softmax warps, registers)
+//     dS = p (dP - delta)  -> tensor memory, 16 bit        (head + residual on the bf16 path)
+//     dQ += dS K_c                                         (dS read from tensor memory)
+// delta needs every chunk of the tile before any dS can be formed.  With one chunk (kernel sizes
+// up to 5: at most 256 keys) a tile is a single unit and dQ reuses the S columns.  With several
+// chunks (at most 192 keys each) the tile is walked twice: units 0..NCH-1 only add up delta,
+// units NCH..2NCH-1 repeat the two score MMAs and accumulate dQ.
+// Twelve warps: 0-7 softmax (warps w and w+4 share 32 queries and split the 16-column blocks),
+// 8 TMA producer, 9 MMA issue, 10-11 idle (register donors).
 #pragma once
 
 namespace na2d_tc {
 
-// ------------------------------------------------------------------------------------ dQ
 template <int D, int KS, bool SPLIT>
 struct DqCfg : Cfg<D, KS, ((TH + KS - 1) * (TW + KS - 1) <= 256 ? 256 : 192)> {
     using B = Cfg<D, KS, ((TH + KS - 1) * (TW + KS - 1) <= 256 ? 256 : 192)>;
-    static constexpr int TMEM_DP = B::NCH == 1 ? 256 : 192;
-    static constexpr int TMEM_DQ = B::NCH == 1 ? 0 : 384;      // single chunk: dQ reuses the S columns
-    // V chunk and dS share one buffer: V is dead once dP is complete, before dS is written.
-    static constexpr int VS_BYTES = B::KV_BYTES > B::P_BYTES ? B::KV_BYTES : B::P_BYTES;
-    static constexpr int BASE = 2 * B::Q_BYTES + B::KV_BYTES + VS_BYTES;
-    // The residual half of dS (bf16 path) gets its own buffer where that fits; otherwise it
-    // reuses the Q / dO tiles, which are dead after the score MMAs of a single-chunk tile.
-    static constexpr bool RES_ALIAS = SPLIT && (BASE + B::P_BYTES + 64 + 1024 > kSmemLimit);
-    static constexpr int RES_BYTES = (SPLIT && !RES_ALIAS) ? B::P_BYTES : 0;
-    static constexpr int SMEM = BASE + RES_BYTES + 64 + 1024;
-    static_assert(!RES_ALIAS || (B::NCH == 1 && 2 * B::Q_BYTES >= B::P_BYTES), "residual buffer does not fit");
+    static constexpr bool ONE = B::NCH == 1;
+    static constexpr int UNITS = ONE ? 1 : 2 * B::NCH;                 // units per tile
+    static constexpr int TMEM_S = 0;
+    static constexpr int TMEM_DP = ONE ? 256 : 192;
+    static constexpr int TMEM_DQ = ONE ? 0 : 384;                      // one chunk: dQ reuses the S columns
+    static constexpr int TMEM_DSH = TMEM_DP;                           // dS (head) over dP
+    static constexpr int TMEM_RES = ONE ? 384 : 0;                     // dS residual: upper dP half / over S
+    static constexpr int FIXED = 2 * B::Q_BYTES + 2 * 2 * 128 * 4 /*delta exchange*/ + 256 + 1024;
+    static constexpr int SMEM = FIXED + 2 * B::KV_BYTES;               // one K chunk, one V chunk
+    static constexpr int NB16 = (B::NKP + 15) / 16;
     static_assert(SMEM <= kSmemLimit, "dQ kernel shared memory");
+    static_assert(ONE ? (B::NKP <= 256) : (B::NKP <= 192), "tensor memory layout");
+    static_assert(!SPLIT || B::NKP / 2 <= (ONE ? 128 : 192), "residual operand does not fit");
 };
 
 template <typename DT, int D, int KS>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(384, 1)
 dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
           const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
           const float* __restrict__ lse, DT* __restrict__ d_q, float* __restrict__ delta,
-          const Na2dGeom g, const int tiles_r, const int tiles_c) {
-    constexpr bool SPLIT = IsBf16<DT>::value;         // bf16: dS goes to the MMA as head + residual
+          const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
+    constexpr bool SPLIT = IsBf16<DT>::value;
     using C = DqCfg<D, KS, SPLIT>;
+    constexpr int NCH = C::NCH, UNITS = C::UNITS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sDO = sQ + C::Q_BYTES;
-    uint8_t* sK = sDO + C::Q_BYTES;
-    uint8_t* sVS = sK + C::KV_BYTES;                  // V chunk, then dS
-    uint8_t* sRES = C::RES_ALIAS ? sQ : sVS + C::VS_BYTES;      // residual half of dS
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sVS + C::VS_BYTES + C::RES_BYTES);
-    uint64_t* bar_load = bars + 0;
-    uint64_t* bar_s = bars + 1;
-    uint64_t* bar_o = bars + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+    uint8_t* sK = sDO + C::Q_BYTES;                   // key chunk   [NKP x D]
+    uint8_t* sV = sK + C::KV_BYTES;                   // value chunk [NKP x D]
+    float* x_sum = reinterpret_cast<float*>(sV + C::KV_BYTES);        // [tile parity][half][row]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_sum + 2 * 2 * 128);
+    uint64_t* q_full = bars + 0;             // TMA -> MMA (Q and dO tile)
+    uint64_t* q_empty = bars + 1;            // MMA (commit) -> TMA
+    uint64_t* k_full = bars + 2;
+    uint64_t* k_empty = bars + 3;
+    uint64_t* v_full = bars + 4;
+    uint64_t* v_empty = bars + 5;
+    uint64_t* s_full = bars + 6;             // MMA (commit) -> softmax: S and dP are complete
+    uint64_t* s_free = bars + 7;             // softmax -> MMA: S and dP have been read (delta-only units)
+    uint64_t* p_full = bars + 8;             // softmax -> MMA: dS is in tensor memory
+    uint64_t* dq_full = bars + 9;            // MMA (commit) -> softmax (epilogue)
+    uint64_t* dq_free = bars + 10;           // softmax -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
-    const int tid = threadIdx.x, warp = tid >> 5;
-    int t = blockIdx.x;
-    const int tc = t % tiles_c;
-    t /= tiles_c;
-    const int tr = t % tiles_r;
-    const int bn = t / tiles_r;
-    const int r0 = tr * TH, c0 = tc * TW;
-    const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
-    const int box_c0 = na2d_ws(c0, g.W, KS);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const bool want_dq = d_q != nullptr;
 
     if (tid == 0) {
         *abort_flag = 0;
-        mbar_init(bar_load, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
+        mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
+        mbar_init(k_full, 1);
+        mbar_init(k_empty, 1);
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        mbar_init(s_full, 1);
+        mbar_init(s_free, 8);
+        mbar_init(p_full, 8);
+        mbar_init(dq_full, 1);
+        mbar_init(dq_free, 8);
         mbar_fence_init();
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_do);
@@ -80,16 +91,15 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     }
     if (warp == 0) {
         __syncwarp();
-        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
-    // K rows [NK, NKP) are contraction rows of dQ = dS K and are never written by TMA: zero them.
-    // (The same rows of the V buffer only feed masked columns of dP and need no care.)
+    // K rows [NK, NKP) are contraction rows of dQ = dS K that TMA never writes: zero them once.
     if constexpr (C::NKP > C::NK) {
         constexpr int pad16 = (C::NKP - C::NK) * C::ROWB / 16;
-        for (int i = tid; i < C::NS * pad16; i += 128) {
-            const int which = i / pad16, off = i - which * pad16;
-            st_shared_v4(smem_u32(sK + which * C::KV_SLAB + C::NK * C::ROWB + off * 16), 0u, 0u, 0u, 0u);
+        for (int i = tid; i < C::NS * pad16; i += 384) {
+            const int slab = i / pad16, off = i - slab * pad16;
+            st_shared_v4(smem_u32(sK + slab * C::KV_SLAB + C::NK * C::ROWB + off * 16), 0u, 0u, 0u, 0u);
         }
         fence_proxy_async();
     }
@@ -97,184 +107,298 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 
-    const int qr_raw = r0 + (tid / TW), qc_raw = c0 + (tid % TW);
-    const bool q_valid = qr_raw < g.Hq && qc_raw < g.W;
-    const int qr = min(qr_raw, g.Hq - 1), qc = min(qc_raw, g.W - 1);
-    const size_t qi = (static_cast<size_t>(bn) * g.Hq + qr) * g.W + qc;
-    const int wr = na2d_ws(g.q_row0 + qr, g.Hg, KS) - g.kv_row0 - box_r0;
-    const int wc = na2d_ws(qc, g.W, KS) - box_c0;
-    const uint32_t row_mask = ((1u << KS) - 1u) << wr;
-    const uint32_t col_mask = ((1u << KS) - 1u) << wc;
-    const int wr_lo = __shfl_sync(0xffffffffu, wr, 0);
-    const int wr_hi = __shfl_sync(0xffffffffu, wr, 31);
-    const float lse2 = lse[qi] * kLog2e;
-
-    constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
-    constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
-    uint32_t ph_load = 0, ph_s = 0, ph_o = 0;
-
-    // Loads chunk `ch` of K and V (plus Q and dO when `with_q`) and issues S = Q K^T, dP = dO V^T.
-    auto load_and_score = [&](int ch, bool with_q) {
-        const uint32_t kv_bytes = 2u * C::NS * C::NK * C::ROWB;
-        mbar_expect_tx(bar_load, kv_bytes + (with_q ? 2u * C::Q_BYTES : 0u));
-#pragma unroll
-        for (int s = 0; s < C::NS; ++s) {
-            if (with_q) {
-                tma_load_4d(sQ + s * C::Q_SLAB, &tm_q, bar_load, s * 64, c0, r0, bn);
-                tma_load_4d(sDO + s * C::Q_SLAB, &tm_do, bar_load, s * 64, c0, r0, bn);
-            }
-            tma_load_4d(sK + s * C::KV_SLAB, &tm_k, bar_load, s * 64, box_c0, box_r0 + ch * C::RC, bn);
-            tma_load_4d(sVS + s * C::KV_SLAB, &tm_v, bar_load, s * 64, box_c0, box_r0 + ch * C::RC, bn);
-        }
-        mbar_wait(bar_load, ph_load, abort_flag, kErrLoadWait);
-        ph_load ^= 1u;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const int slab = (kk * 16) / C::SLAB_C, in_slab = (kk * 16) % C::SLAB_C;
-            const uint64_t aq = smem_desc(smem_u32(sQ + slab * C::Q_SLAB) + in_slab * 2, 16, C::ATOM, C::SWZ);
-            const uint64_t bk = smem_desc(smem_u32(sK + slab * C::KV_SLAB) + in_slab * 2, 16, C::ATOM, C::SWZ);
-            umma_ss(tmem_base + C::TMEM_S, aq, bk, idesc_s, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const int slab = (kk * 16) / C::SLAB_C, in_slab = (kk * 16) % C::SLAB_C;
-            const uint64_t ag = smem_desc(smem_u32(sDO + slab * C::Q_SLAB) + in_slab * 2, 16, C::ATOM, C::SWZ);
-            const uint64_t bv = smem_desc(smem_u32(sVS + slab * C::KV_SLAB) + in_slab * 2, 16, C::ATOM, C::SWZ);
-            umma_ss(tmem_base + C::TMEM_DP, ag, bv, idesc_s, kk > 0);
-        }
-        umma_commit(bar_s);
+    auto decode = [&](int i, int& bn, int& r0, int& c0) {
+        int t = (int)blockIdx.x + i * (int)gridDim.x;
+        const int tc = t % tiles_c;
+        t /= tiles_c;
+        r0 = (t % tiles_r) * TH;
+        c0 = tc * TW;
+        bn = t / tiles_r;
     };
+    // A unit u of a tile works on chunk u % NCH; units >= NCH (or the only unit) form dS and dQ.
+    // Without a dQ output only the delta units run.
+    const int units_run = want_dq ? UNITS : (C::ONE ? 1 : NCH);
 
-    // ---- phase A: delta = sum_j p_j dp_j -------------------------------------------------------------
-    float dl = 0.f;
+    if (warp == 8) {
+        // ------------------------------------------------------------------ producer
+        reg_dec<kRegsDonor>();
+        if (lane == 0) {
+            uint32_t n = 0;
+            for (int i = 0; i < n_my; ++i) {
+                int bn, r0, c0;
+                decode(i, bn, r0, c0);
+                const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
+                const int box_c0 = na2d_ws(c0, g.W, KS);
+                mbar_wait(q_empty, (i & 1) ^ 1, abort_flag, kErrLoadWait);
+                mbar_expect_tx(q_full, 2u * C::Q_BYTES);
 #pragma unroll
-    for (int ch = 0; ch < C::NCH; ++ch) {
-        if (tid == 0) load_and_score(ch, ch == 0);
-        __syncwarp();
-        mbar_wait(bar_s, ph_s, abort_flag, kErrMmaWait);
-        ph_s ^= 1u;
-        tc_fence_after();
+                for (int s = 0; s < C::NS; ++s) {
+                    tma_load_4d(sQ + s * C::Q_SLAB, &tm_q, q_full, s * 64, c0, r0, bn);
+                    tma_load_4d(sDO + s * C::Q_SLAB, &tm_do, q_full, s * 64, c0, r0, bn);
+                }
+                for (int u = 0; u < units_run; ++u, ++n) {
+                    const int c = u % NCH;
+                    mbar_wait(v_empty, (n & 1) ^ 1, abort_flag, kErrLoadWait);
+                    mbar_expect_tx(v_full, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
-        for (int b = 0; b < C::NB; ++b) {
-            const int row_first = ch * C::RC + (32 * b) / C::HW;
-            const int last_col = (32 * b + 31 < C::NK - 1) ? 32 * b + 31 : C::NK - 1;
-            const int row_last = ch * C::RC + last_col / C::HW;
-            if (32 * b < C::NK && row_last >= wr_lo && row_first < wr_hi + KS) {
-                uint32_t s[32], dp[32];
-                tmem_ld_32x32(tmem_lane + C::TMEM_S + 32 * b, s);
-                tmem_ld_32x32(tmem_lane + C::TMEM_DP + 32 * b, dp);
-                tmem_ld_wait();
+                    for (int s = 0; s < C::NS; ++s)
+                        tma_load_4d(sV + s * C::KV_SLAB, &tm_v, v_full, s * 64, box_c0, box_r0 + c * C::RC, bn);
+                    mbar_wait(k_empty, (n & 1) ^ 1, abort_flag, kErrLoadWait);
+                    mbar_expect_tx(k_full, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int j = 32 * b + e;
-                    if (j < C::NK) {
-                        const int hr = ch * C::RC + j / C::HW, hc = j % C::HW;
-                        const bool ok = ((row_mask >> hr) & 1u) && ((col_mask >> hc) & 1u);
-                        const float p = fast_exp2(fmaf(__uint_as_float(s[e]), kLog2e, -lse2));
-                        dl += ok ? p * __uint_as_float(dp[e]) : 0.f;
-                    }
+                    for (int s = 0; s < C::NS; ++s)
+                        tma_load_4d(sK + s * C::KV_SLAB, &tm_k, k_full, s * 64, box_c0, box_r0 + c * C::RC, bn);
                 }
             }
         }
-        if (C::NCH > 1) {
-            tc_fence_before();
-            __syncthreads();          // the chunk buffers and the S / dP columns are free again
-        }
-    }
-    if (q_valid) delta[qi] = dl;
-
-    // ---- phase B: dS -> shared, dQ += dS K -------------------------------------------------------------
-    if (d_q != nullptr) {
-#pragma unroll
-        for (int ch = 0; ch < C::NCH; ++ch) {
-            if (C::NCH > 1) {
-                if (tid == 0) load_and_score(ch, false);
-                __syncwarp();
-                mbar_wait(bar_s, ph_s, abort_flag, kErrMmaWait);
-                ph_s ^= 1u;
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issue
+        reg_dec<kRegsDonor>();
+        const bool leader = lane == 0;
+        constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
+        constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
+        constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
+        const uint32_t q_lo = smem_desc_lo(smem_u32(sQ), 16), g_lo = smem_desc_lo(smem_u32(sDO), 16);
+        const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16), v_lo = smem_desc_lo(smem_u32(sV), 16);
+        const uint32_t km_lo = smem_desc_lo(smem_u32(sK), C::KV_SLAB);
+        uint32_t n = 0, n_free = 0, n_p = 0;          // units, delta-only units, dS units so far
+        for (int i = 0; i < n_my; ++i) {
+            mbar_wait(q_full, i & 1, abort_flag, kErrLoadWait);
+            for (int u = 0; u < units_run; ++u, ++n) {
+                const bool forms_ds = want_dq && (C::ONE || u >= NCH);
+                mbar_wait(k_full, n & 1, abort_flag, kErrLoadWait);
+                mbar_wait(v_full, n & 1, abort_flag, kErrLoadWait);
+                // the accumulators the score MMAs overwrite must have been read
+                if (u > 0 && !(C::ONE) && u <= NCH) {            // previous unit was delta-only
+                    mbar_wait(s_free, (n_free & 1) ^ 1, abort_flag, kErrMmaWait);
+                }
+                if (u == 0 && i > 0) {
+                    if (C::ONE || !want_dq) {
+                        // previous tile: its last unit either left dQ over S (epilogue must have read
+                        // it) or was delta-only (S must have been read)
+                        if (want_dq) mbar_wait(dq_free, (i & 1) ^ 1, abort_flag, kErrMmaWait);
+                        else mbar_wait(s_free, (n_free & 1) ^ 1, abort_flag, kErrMmaWait);
+                    }
+                }
                 tc_fence_after();
+                if (leader) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        constexpr int kPerSlab = C::SLAB_C / 16;
+                        const int slab = kk / kPerSlab, in_slab = kk % kPerSlab;
+                        umma_ss(tmem_base + C::TMEM_S, desc64(hi, q_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
+                                desc64(hi, k_lo + ((slab * C::KV_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        constexpr int kPerSlab = C::SLAB_C / 16;
+                        const int slab = kk / kPerSlab, in_slab = kk % kPerSlab;
+                        umma_ss(tmem_base + C::TMEM_DP, desc64(hi, g_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
+                                desc64(hi, v_lo + ((slab * C::KV_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
+                    }
+                    umma_commit(s_full);
+                    umma_commit(v_empty);
+                    if (!forms_ds) umma_commit(k_empty);
+                    if (u == units_run - 1) umma_commit(q_empty);     // last score MMAs of the tile
+                }
+                __syncwarp();
+                if (!forms_ds) { ++n_free; continue; }
+                mbar_wait(p_full, n_p & 1, abort_flag, kErrMmaWait);
+                ++n_p;
+                if (!C::ONE && u == NCH && i > 0) mbar_wait(dq_free, (i & 1) ^ 1, abort_flag, kErrMmaWait);
+                tc_fence_after();
+                if (leader) {
+                    const uint32_t acc = (!C::ONE && u > NCH) ? 1u : 0u;
+#pragma unroll
+                    for (int kk = 0; kk < C::NKP / 16; ++kk)
+                        umma_ts(tmem_base + C::TMEM_DQ, tmem_base + C::TMEM_DSH + 8 * kk,
+                                desc64(hi, km_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
+                    if (SPLIT) {
+#pragma unroll
+                        for (int kk = 0; kk < C::NKP / 16; ++kk)
+                            umma_ts(tmem_base + C::TMEM_DQ, tmem_base + C::TMEM_RES + 8 * kk,
+                                    desc64(hi, km_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, 1u);
+                    }
+                    umma_commit(k_empty);
+                    if (u == units_run - 1) umma_commit(dq_full);
+                }
+                __syncwarp();
             }
+        }
+    } else if (warp >= 10) {
+        reg_dec<kRegsDonor>();
+    } else {
+        // ------------------------------------------------------------------ softmax warps
+        reg_inc<kRegsSoftmax>();
+        const int quarter = warp & 3, half = warp >> 2;
+        const int row = quarter * 32 + lane;                 // query of the tile = tensor-memory lane
+        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        constexpr int DH = D / 2;                            // output columns stored by this half
+        constexpr int NBH = (C::NB16 + 1) / 2;               // own blocks at most
+        constexpr int kRows = (32 / TW - 1 + KS) < C::RC ? (32 / TW - 1 + KS) : C::RC;
+        constexpr int kBlocks = (kRows * C::HW - 1) / 16 + 2;
+        constexpr int NACT = (kBlocks + 1) / 2 < NBH ? (kBlocks + 1) / 2 : NBH;
+
+        uint32_t n = 0, n_x = 0;                             // units, delta exchanges so far
+        for (int i = 0; i < n_my; ++i) {
+            int bn, r0, c0;
+            decode(i, bn, r0, c0);
+            const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
+            const int box_c0 = na2d_ws(c0, g.W, KS);
+            const int qr_raw = r0 + (row / TW), qc_raw = c0 + (row % TW);
+            const bool q_valid = qr_raw < g.Hq && qc_raw < g.W;
+            const int qr = min(qr_raw, g.Hq - 1), qc = min(qc_raw, g.W - 1);
+            const size_t qi = (static_cast<size_t>(bn) * g.Hq + qr) * g.W + qc;
+            const int wr = na2d_ws(g.q_row0 + qr, g.Hg, KS) - g.kv_row0 - box_r0;   // in [0, TH)
+            const int wc = na2d_ws(qc, g.W, KS) - box_c0;                            // in [0, TW)
+            const int wr_lo = __shfl_sync(0xffffffffu, wr, 0);
+            const int wr_hi = __shfl_sync(0xffffffffu, wr, 31);
+            const float lse2 = lse[qi] * kLog2e;
+            float dl_part = 0.f, dl = 0.f;                   // this half's part of delta; delta
+
+            for (int u = 0; u < units_run; ++u, ++n) {
+                const int ch = u % NCH;
+                const bool forms_ds = want_dq && (C::ONE || u >= NCH);
+                const bool adds_delta = C::ONE || u < NCH;
+                const int row_off = ch * C::RC;
+                const int j_lo = max(wr_lo - row_off, 0) * C::HW;
+                const int j_hi = min(min(wr_hi + KS - row_off, C::RC) * C::HW, C::NK);       // exclusive
+                const int b_hi = (max(j_hi, 0) + 15) >> 4;
+                const int bi_lo = ((j_lo >> 4) - half + 1) >> 1;
+
+                mbar_wait(s_full, n & 1, abort_flag, kErrMmaWait);
+                tc_fence_after();
+                uint32_t s[NACT][16], dp[NACT][16];
+                uint32_t vmask[NACT];
 #pragma unroll
-            for (int b = 0; b < C::NB; ++b) {
-                const int row_first = ch * C::RC + (32 * b) / C::HW;
-                const int last_col = (32 * b + 31 < C::NK - 1) ? 32 * b + 31 : C::NK - 1;
-                const int row_last = ch * C::RC + last_col / C::HW;
-                uint32_t w[16], w2[16];
-                if (32 * b < C::NK && row_last >= wr_lo && row_first < wr_hi + KS) {
-                    uint32_t s[32], dp[32];
-                    tmem_ld_32x32(tmem_lane + C::TMEM_S + 32 * b, s);
-                    tmem_ld_32x32(tmem_lane + C::TMEM_DP + 32 * b, dp);
-                    tmem_ld_wait();
-                    float ds[32];
+                for (int a = 0; a < NACT; ++a) {
+                    const int blk = half + 2 * (bi_lo + a);
+                    if (blk < b_hi) {                                        // warp-uniform
+                        tmem_ld_32x16(tmem_lane + C::TMEM_S + 16 * blk, s[a]);
+                        tmem_ld_32x16(tmem_lane + C::TMEM_DP + 16 * blk, dp[a]);
+                    }
+                }
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int j = 32 * b + e;
-                        ds[e] = 0.f;
-                        if (j < C::NK) {
-                            const int hr = ch * C::RC + j / C::HW, hc = j % C::HW;
-                            const bool ok = ((row_mask >> hr) & 1u) && ((col_mask >> hc) & 1u);
-                            const float p = fast_exp2(fmaf(__uint_as_float(s[e]), kLog2e, -lse2));
-                            ds[e] = ok ? p * (__uint_as_float(dp[e]) - dl) : 0.f;
+                for (int a = 0; a < NACT; ++a) {                             // validity masks, loads in flight
+                    const int blk = half + 2 * (bi_lo + a);
+                    uint32_t m = 0;
+#pragma unroll
+                    for (int w = 0; w < KS; ++w) {
+                        const int r = wr + w - row_off;                       // chunk row of window row w
+                        const int rel = r * C::HW + wc - 16 * blk;            // its first column, relative to the block
+                        const uint32_t seg = (1u << KS) - 1u;
+                        const uint32_t bits = rel >= 0 ? (seg << (rel & 31)) : (seg >> ((-rel) & 31));
+                        if (r >= 0 && r < C::RC && rel > -KS && rel < 16) m |= bits;
+                    }
+                    vmask[a] = (blk < b_hi) ? (m & 0xffffu) : 0u;
+                }
+                tmem_ld_wait();
+
+                // p = exp(s - lse) in place of s; this half's part of delta
+                float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+                for (int a = 0; a < NACT; ++a) {
+                    if (half + 2 * (bi_lo + a) < b_hi) {
+#pragma unroll
+                        for (int e = 0; e < 16; e += 2) {
+                            const float p0 = ((vmask[a] >> e) & 1u)
+                                                 ? fast_exp2(fmaf(__uint_as_float(s[a][e]), kLog2e, -lse2)) : 0.f;
+                            const float p1 = ((vmask[a] >> (e + 1)) & 1u)
+                                                 ? fast_exp2(fmaf(__uint_as_float(s[a][e + 1]), kLog2e, -lse2)) : 0.f;
+                            s[a][e] = __float_as_uint(p0);
+                            s[a][e + 1] = __float_as_uint(p1);
+                            // masked columns may hold anything (padding keys): keep them out by
+                            // selection, never by multiplying with zero
+                            if (!((vmask[a] >> e) & 1u)) dp[a][e] = 0u;
+                            if (!((vmask[a] >> (e + 1)) & 1u)) dp[a][e + 1] = 0u;
+                            d0 = fmaf(p0, __uint_as_float(dp[a][e]), d0);
+                            d1 = fmaf(p1, __uint_as_float(dp[a][e + 1]), d1);
                         }
                     }
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        w[e] = pack2<DT>(ds[2 * e], ds[2 * e + 1]);
-                        w2[e] = SPLIT ? pack2_residual_bf16(ds[2 * e], ds[2 * e + 1], w[e]) : 0u;
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) { w[e] = 0u; w2[e] = 0u; }
                 }
-                store_operand_block(smem_u32(sVS), C::P_SLAB, tid, b, w);
-                if (SPLIT) store_operand_block(smem_u32(sRES), C::P_SLAB, tid, b, w2);
-            }
-            fence_proxy_async();
-            tc_fence_before();
-            __syncthreads();
-            if (tid == 0) {
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < C::NKP / 16; ++kk) {
-                    const uint64_t a = smem_desc(smem_u32(sVS + (kk >> 2) * C::P_SLAB) + (kk & 3) * 32, 16, 1024, 2u);
-                    const uint64_t bk = smem_desc(smem_u32(sK) + kk * 16 * C::ROWB, C::KV_SLAB, C::ATOM, C::SWZ);
-                    umma_ss(tmem_base + C::TMEM_DQ, a, bk, idesc_o, (ch > 0) || (kk > 0));
-                }
-                if (SPLIT) {
-#pragma unroll
-                    for (int kk = 0; kk < C::NKP / 16; ++kk) {
-                        const uint64_t a = smem_desc(smem_u32(sRES + (kk >> 2) * C::P_SLAB) + (kk & 3) * 32, 16, 1024, 2u);
-                        const uint64_t bk = smem_desc(smem_u32(sK) + kk * 16 * C::ROWB, C::KV_SLAB, C::ATOM, C::SWZ);
-                        umma_ss(tmem_base + C::TMEM_DQ, a, bk, idesc_o, 1u);
-                    }
-                }
-                umma_commit(bar_o);
-            }
-            __syncwarp();
-            mbar_wait(bar_o, ph_o, abort_flag, kErrMmaWait);
-            ph_o ^= 1u;
-            tc_fence_after();
-        }
+                if (adds_delta) dl_part += d0 + d1;
 
-        DT* row = d_q + qi * D;
-#pragma unroll
-        for (int piece = 0; piece < D / 32; ++piece) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_lane + C::TMEM_DQ + 32 * piece, v);
-            tmem_ld_wait();
-            if (q_valid) {
-#pragma unroll
-                for (int gI = 0; gI < 4; ++gI) {
-                    uint4 pk;
-                    pk.x = pack2<DT>(__uint_as_float(v[8 * gI + 0]), __uint_as_float(v[8 * gI + 1]));
-                    pk.y = pack2<DT>(__uint_as_float(v[8 * gI + 2]), __uint_as_float(v[8 * gI + 3]));
-                    pk.z = pack2<DT>(__uint_as_float(v[8 * gI + 4]), __uint_as_float(v[8 * gI + 5]));
-                    pk.w = pack2<DT>(__uint_as_float(v[8 * gI + 6]), __uint_as_float(v[8 * gI + 7]));
-                    *reinterpret_cast<uint4*>(row + 32 * piece + 8 * gI) = pk;
+                if (adds_delta && (C::ONE || u == NCH - 1)) {
+                    // all chunks seen: add the partner's part; both now hold delta
+                    x_sum[((n_x & 1) * 2 + half) * 128 + row] = dl_part;
+                    bar_sync(1 + quarter, 64);
+                    dl = dl_part + x_sum[((n_x & 1) * 2 + (half ^ 1)) * 128 + row];
+                    ++n_x;
+                    if (q_valid && half == 0) delta[qi] = dl;
+                } else {
+                    // the partner must have read its blocks before 16-bit operands go over them
+                    bar_sync(1 + quarter, 64);
                 }
+
+                if (!forms_ds) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(s_free);
+                    continue;
+                }
+
+                // dS = p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path)
+#pragma unroll
+                for (int a = 0; a < NACT; ++a) {
+                    const int blk = half + 2 * (bi_lo + a);
+                    if (blk < b_hi) {
+                        uint32_t wd[8], wr2[8];
+#pragma unroll
+                        for (int e2 = 0; e2 < 8; ++e2) {
+                            const float ds0 = ((vmask[a] >> (2 * e2)) & 1u)
+                                ? __uint_as_float(s[a][2 * e2]) * (__uint_as_float(dp[a][2 * e2]) - dl) : 0.f;
+                            const float ds1 = ((vmask[a] >> (2 * e2 + 1)) & 1u)
+                                ? __uint_as_float(s[a][2 * e2 + 1]) * (__uint_as_float(dp[a][2 * e2 + 1]) - dl) : 0.f;
+                            wd[e2] = pack2<DT>(ds0, ds1);
+                            wr2[e2] = SPLIT ? pack2_residual_bf16(ds0, ds1, wd[e2]) : 0u;
+                        }
+                        tmem_st_32x8(tmem_lane + C::TMEM_DSH + 8 * blk, wd);
+                        if (SPLIT) tmem_st_32x8(tmem_lane + C::TMEM_RES + 8 * blk, wr2);
+                    }
+                }
+                {   // own blocks outside the range hold zeros
+                    const uint32_t z[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+                    for (int bi = 0; bi < NBH; ++bi) {
+                        const int blk = half + 2 * bi;
+                        const bool in_range = bi >= bi_lo && bi < bi_lo + NACT && blk < b_hi;
+                        if (!in_range && 16 * blk < C::NKP) {
+                            tmem_st_32x8(tmem_lane + C::TMEM_DSH + 8 * blk, z);
+                            if (SPLIT) tmem_st_32x8(tmem_lane + C::TMEM_RES + 8 * blk, z);
+                        }
+                    }
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full);
+            }
+
+            if (want_dq) {
+                // ---- epilogue: this half's columns of the thread's dQ row
+                mbar_wait(dq_full, i & 1, abort_flag, kErrMmaWait);
+                tc_fence_after();
+                DT* out = d_q + qi * D + half * DH;
+#pragma unroll
+                for (int piece = 0; piece < DH / 16; ++piece) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(tmem_lane + C::TMEM_DQ + half * DH + 16 * piece, v);
+                    tmem_ld_wait();
+                    if (q_valid) {
+#pragma unroll
+                        for (int gI = 0; gI < 2; ++gI) {
+                            uint4 pk;
+                            pk.x = pack2<DT>(__uint_as_float(v[8 * gI + 0]), __uint_as_float(v[8 * gI + 1]));
+                            pk.y = pack2<DT>(__uint_as_float(v[8 * gI + 2]), __uint_as_float(v[8 * gI + 3]));
+                            pk.z = pack2<DT>(__uint_as_float(v[8 * gI + 4]), __uint_as_float(v[8 * gI + 5]));
+                            pk.w = pack2<DT>(__uint_as_float(v[8 * gI + 6]), __uint_as_float(v[8 * gI + 7]));
+                            *reinterpret_cast<uint4*>(out + 16 * piece + 8 * gI) = pk;
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dq_free);
             }
         }
     }
@@ -283,14 +407,13 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, C::TMEM_COLS);
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
-// ------------------------------------------------------------------------------------ launchers
 template <typename DT, int D, int KS>
 int launch_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-              const void* d_o, void* d_q, float* delta, cudaStream_t st, int* launched) {
+              const void* d_o, void* d_q, float* delta, int device, cudaStream_t st, int* launched) {
     using C = DqCfg<D, KS, IsBf16<DT>::value>;
     CUtensorMap tq, tg, tk, tv;
     int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
@@ -304,17 +427,19 @@ int launch_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const 
     auto kern = dq_kernel<DT, D, KS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return NA2D_ERR_CUDA;
-    kern<<<(unsigned)tiles, 128, C::SMEM, st>>>(tq, tg, tk, tv, lse, (DT*)d_q, delta, g, tiles_r, tiles_c);
+    const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
+    kern<<<grid, 384, C::SMEM, st>>>(tq, tg, tk, tv, lse, (DT*)d_q, delta, g, tiles_r, tiles_c, (int)tiles);
     *launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }
 
 inline int backward_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const void* /*o*/,
-                       const float* lse, const void* d_o, void* d_q, float* delta, int, cudaStream_t st, int* launched) {
+                       const float* lse, const void* d_o, void* d_q, float* delta, int device, cudaStream_t st,
+                       int* launched) {
     if (dtype == NA2D_BF16) {
-        NA2D_TC_DISPATCH_D(launch_dq, __nv_bfloat16, g, dtype, q, k, v, lse, d_o, d_q, delta, st, launched)
+        NA2D_TC_DISPATCH_D(launch_dq, __nv_bfloat16, g, dtype, q, k, v, lse, d_o, d_q, delta, device, st, launched)
     } else {
-        NA2D_TC_DISPATCH_D(launch_dq, __half, g, dtype, q, k, v, lse, d_o, d_q, delta, st, launched)
+        NA2D_TC_DISPATCH_D(launch_dq, __half, g, dtype, q, k, v, lse, d_o, d_q, delta, device, st, launched)
     }
 }
 

@@ -348,8 +348,9 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                             for (int h = 0; h < 2; ++h) {
                                 const int e = 2 * e2 + h;
                                 const float pe = fast_exp2(fmaf(__uint_as_float(s[a][e]), kLog2e, -l2[e]));
-                                p[h] = ((vmask[a] >> e) & 1u) ? pe : 0.f;
-                                ds[h] = p[h] * (__uint_as_float(dp[a][e]) - dl[e]);
+                                const bool ok = (vmask[a] >> e) & 1u;      // select, never multiply by zero
+                                p[h] = ok ? pe : 0.f;
+                                ds[h] = ok ? pe * (__uint_as_float(dp[a][e]) - dl[e]) : 0.f;
                             }
                             wp[e2] = pack2<DT>(p[0], p[1]);
                             wd[e2] = pack2<DT>(ds[0], ds[1]);
