@@ -191,6 +191,71 @@ def run_reference_arm(args, wl_name, wl):
     print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------------------- row-sharded arm
+def run_row_sharded(args, wl, dev, rank, world):
+    """One huge image split by rows over the ranks (strong scaling): every step exchanges the
+    kernel_size//2-row K/V halo with the neighbours, runs forward + backward on the band through
+    a row view, and reduces the dK/dV halo.  Device-timed, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    import e_natten_b200 as na
+    from e_natten_b200 import functional as F, sharding
+
+    B, N, H, W, C, ks, dtype, seed, scale, q_scale = wl
+    dt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
+    sh = sharding.plan_row_shard(H, world, rank, ks)
+    g = torch.Generator(device=dev).manual_seed(seed + 1000 * rank)
+    mk = lambda: (torch.randn((B, N, sh.R, W, C), generator=g, device=dev, dtype=torch.float32) * scale).to(dt)
+    q, k, v, d_o = mk(), mk(), mk(), mk()
+    o, d_q = torch.empty_like(q), torch.empty_like(q)
+    lse = torch.empty((B, N, sh.R, W), dtype=torch.float32, device=dev)
+    delta = torch.empty_like(lse)
+    rows = sh.rows()
+
+    def step():
+        k_ext, v_ext = sharding.exchange_kv_halo(k, v, sh)
+        F.forward_into(q, k_ext, v_ext, o, lse, ks, rows=rows)
+        dk_ext, dv_ext = torch.empty_like(k_ext), torch.empty_like(v_ext)
+        F.backward_dq_into(q, k_ext, v_ext, o, lse, d_o, d_q, delta, ks, rows=rows)
+        F.backward_dkdv_into(q, k_ext, v_ext, lse, d_o, delta, dk_ext, dv_ext, ks, rows=rows)
+        return sharding.reduce_dkdv_halo(dk_ext, dv_ext, sh)
+
+    for _ in range(args.warmup):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    na.check_kernels(dev)
+    launches0 = na.launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    if rank == 0:
+        fl = 3.5 * flops_fwd(B, N, H, W, C, ks)
+        esize = torch.empty((), dtype=dt).element_size()
+        ab = algorithmic_bytes(B, N, H, W, C, esize)
+        hbm_peak, _, peak_kind = measured_peaks()
+        halo = 2 * (ks // 2) * W * C * esize * B * N       # one tensor, both sides of an interior band
+        print(json.dumps({
+            "metric": "effective_tflops_fwd_bwd", "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": args.workload, "B": B, "heads": N, "H": H, "W": W, "head_dim": C, "kernel_size": ks,
+                       "sharding": f"rows, {sh.R} per GPU, {ks // 2}-row K/V halo exchange + dK/dV halo reduction (NCCL p2p)",
+                       "halo_bytes_per_step_per_gpu": 4 * halo, "l2": "inputs larger than L2"},
+            "roofline_step": {"bound": "hbm", "achieved": ab["step"] / world / (ms * 1e-3) / 1e9, "peak": hbm_peak,
+                              "unit": "GB/s", "frac": ab["step"] / world / (ms * 1e-3) / 1e9 / hbm_peak,
+                              "peak_source": peak_kind},
+            "gpu_launches": na.launch_count() - launches0}), flush=True)
+    dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -228,6 +293,10 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.workload == "c5" and world > 1:        # the single huge image is split by rows
+        run_row_sharded(args, wl, dev, rank, world)
+        return
 
     B, N, H, W, C, ks, dtype, seed, scale, q_scale = wl
     dt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
