@@ -22,6 +22,17 @@ int cuda_fail(cudaError_t e, const char* what) {
     return NA2D_ERR_CUDA;
 }
 
+// Failure of a tcgen05 launcher: either a runtime error or a failed tensor-map encode (a driver call).
+int tc_fail(const char* what) {
+    int& drv = na2d_tc::last_driver_result();
+    if (drv != 0) {
+        snprintf(t_cuda_err, sizeof(t_cuda_err), "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, drv);
+        drv = 0;
+        return NA2D_ERR_CUDA;
+    }
+    return cuda_fail(cudaGetLastError(), what);
+}
+
 #define NA2D_CUDA(call)                                        \
     do {                                                       \
         cudaError_t e__ = (call);                              \
@@ -29,12 +40,16 @@ int cuda_fail(cudaError_t e, const char* what) {
     } while (0)
 
 // Makes `device` current for the scope and restores the previous device afterwards.
+// cudaSetDevice is called even when `device` already is the thread's current device: a thread that
+// has made no runtime call yet (an autograd worker thread, for one) reports device 0 as current
+// without having its context bound, and the driver call that encodes tensor maps needs a bound
+// context.
 struct DeviceScope {
     int prev = -1;
     cudaError_t err = cudaSuccess;
     explicit DeviceScope(int device) {
         err = cudaGetDevice(&prev);
-        if (err == cudaSuccess && prev != device) err = cudaSetDevice(device);
+        if (err == cudaSuccess) err = cudaSetDevice(device);
     }
     ~DeviceScope() {
         int cur = -1;
@@ -234,7 +249,7 @@ int na2d_forward(const void* q, const void* k, const void* v, void* o, float* ls
         int launched = 0;
         rc = na2d_tc::forward(p.g, dtype, q, k, v, o, lse, device, st, &launched);
         g_launches.fetch_add(launched);
-        if (rc == NA2D_ERR_CUDA) return cuda_fail(cudaGetLastError(), "tcgen05 forward launch");
+        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 forward launch");
         return rc;
     }
     switch (dtype) {
@@ -255,7 +270,7 @@ int na2d_backward_dq(const void* q, const void* k, const void* v, const void* o,
         int launched = 0;
         rc = na2d_tc::backward_dq(p.g, dtype, q, k, v, o, lse, d_o, d_q, delta, device, st, &launched);
         g_launches.fetch_add(launched);
-        if (rc == NA2D_ERR_CUDA) return cuda_fail(cudaGetLastError(), "tcgen05 dQ launch");
+        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 dQ launch");
         return rc;
     }
     switch (dtype) {
@@ -275,7 +290,7 @@ int na2d_backward_dkdv(const void* q, const void* k, const void* v, const float*
         int launched = 0;
         rc = na2d_tc::backward_dkdv(p.g, dtype, q, k, v, lse, d_o, delta, d_k, d_v, device, st, &launched);
         g_launches.fetch_add(launched);
-        if (rc == NA2D_ERR_CUDA) return cuda_fail(cudaGetLastError(), "tcgen05 dK/dV launch");
+        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 dK/dV launch");
         return rc;
     }
     switch (dtype) {

@@ -133,6 +133,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// CUresult of the last failed tensor-map encode on this thread (0 if none), for error messages.
+inline int& last_driver_result() {
+    thread_local int r = 0;
+    return r;
+}
+
 inline EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = nullptr;
     static std::once_flag once;
@@ -161,6 +167,7 @@ inline int make_map(CUtensorMap* map, const void* base, int dtype, long long BN,
     const CUtensorMapSwizzle sw = slab_c * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) last_driver_result() = (int)r;
     return r == CUDA_SUCCESS ? NA2D_OK : NA2D_ERR_CUDA;
 }
 

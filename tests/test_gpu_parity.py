@@ -302,6 +302,35 @@ def test_autograd_semantics_match_the_reference_entry_point():
     assert_close(lse, rlse, torch.float32, "lse")
 
 
+def test_entry_points_work_from_a_thread_that_made_no_cuda_call():
+    """An autograd worker thread may reach the library before any runtime call has bound the
+    device's context to it; the tensor-core launchers (which encode tensor maps through the
+    driver) must still work there."""
+    import threading
+    q, k, v, d_o = make_inputs((1, 2, 24, 24, 64), torch.bfloat16, 5, q_scale=0.125)
+    o, lse, dq, dk, dv = run_gpu(q, k, v, d_o, 7)
+    qd, kd, vd, gd = (t.to(DEV) for t in (q, k, v, d_o))
+    outs = [torch.empty_like(qd) for _ in range(3)]
+    delta = torch.empty_like(lse)
+    torch.cuda.synchronize()
+    box = {}
+
+    def work():
+        try:
+            na.functional.backward_dq_into(qd, kd, vd, o, lse, gd, outs[0], delta, 7)
+            na.functional.backward_dkdv_into(qd, kd, vd, lse, gd, delta, outs[1], outs[2], 7)
+        except Exception as exc:        # noqa: BLE001 -- reported by the assert below
+            box["exc"] = exc
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert "exc" not in box, box.get("exc")
+    torch.cuda.synchronize()
+    na.check_kernels(DEV)
+    assert torch.equal(outs[0], dq) and torch.equal(outs[1], dk) and torch.equal(outs[2], dv)
+
+
 def test_non_contiguous_inputs_and_grad_output_are_accepted():
     """The reference asserts equal strides (e_natten/triton.py:233-234); accepting strided views
     is a harmless superset."""

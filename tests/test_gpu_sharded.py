@@ -4,6 +4,9 @@ halo reduction over NCCL; the bands must equal the whole-image result computed o
 import datetime
 import os
 import socket
+import sys
+import time
+import traceback
 
 import pytest
 import torch
@@ -54,8 +57,13 @@ def _worker(rank, world, port, shape, ks, dtype, result):
         dist.all_gather_object(oks, ok)
         if rank == 0:
             result.put(oks)
-    finally:
-        dist.destroy_process_group()
+    except BaseException:
+        # leave at once and loudly: the parent sees the exit code and stops the other rank, which
+        # may be waiting for a transfer from this one; tearing the process group down here could block
+        traceback.print_exc()
+        sys.stderr.flush()
+        os._exit(1)
+    dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("shape,ks,dtype", [((1, 2, 64, 40, 64), 7, torch.bfloat16),
@@ -69,7 +77,14 @@ def test_row_sharded_two_gpus(shape, ks, dtype):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, shape, ks, dtype, result)) for r in range(2)]
     for p in procs:
         p.start()
+    deadline = time.time() + 240
+    while any(p.is_alive() for p in procs) and time.time() < deadline:
+        if any(p.exitcode not in (None, 0) for p in procs):
+            break
+        time.sleep(0.2)
     for p in procs:
-        p.join(timeout=300)
+        if p.is_alive():                     # never leave a stuck rank behind: pytest would wait for it at exit
+            p.kill()
+        p.join()
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert result.get(timeout=5) == [True, True]
