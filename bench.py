@@ -17,7 +17,7 @@ The printed JSON line carries
   roofline              the dominant kernel against the measured HBM peak (MEASURED_PEAKS.json),
   roofline_step         the whole step's algorithmic bytes (12T + 2L) against the same peak,
   cpu_baseline          the CPU oracle port timed on this host on a bounded sample,
-  clocks                SM clocks sampled with nvidia-smi during the timed region.
+  clocks                SM clocks and throttle reasons sampled through NVML during the timed region.
 
 `--impl reference` times the CPU port of the reference's algorithm (oracle/) on the host cores,
 since the reference itself is Python that needs its source checkout and a Triton-capable
@@ -62,6 +62,13 @@ def algorithmic_bytes(B, N, H, W, C, esize):
     L = B * N * H * W * 4
     return {"fwd": 4 * T + L, "dq": 6 * T + 2 * L, "dkdv": 6 * T + 2 * L, "bwd": 8 * T + L,
             "step": 12 * T + 2 * L, "T": T, "L": L}
+
+
+# DRAM bytes (read + written) per launch, per byte of one (B, N, H, W, C) tensor, from one ncu
+# capture of workload c2 at side 128 (profiles/tcgen05_fwd_dq_dkdv_c2_bf16.md).  Reads equal the
+# input bytes, so the traffic of the other c2 sides follows in proportion to the tensor size.
+NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"na2d forward": 3.614, "na2d backward dQ": 4.737, "na2d backward dK/dV": 5.490}
+NCU_TRAFFIC_SOURCE = "ncu capture of c2-128 scaled by tensor bytes"
 
 
 def measured_peaks():
@@ -411,6 +418,9 @@ def main():
             "na2d backward dK/dV": (ms_dkdv, ab["dkdv"])}
     dom = max(kern, key=lambda n: kern[n][0])
     dom_ms, dom_bytes = kern[dom]
+    traffic = None
+    if args.workload.startswith("c2-") and dtype in ("bf16", "fp16") and args.path != "simt":
+        traffic = NCU_DRAM_BYTES_PER_TENSOR_BYTE[dom] * ab["T"]
     ach = dom_bytes / (dom_ms * 1e-3) / 1e9
     step_ach = ab["step"] / (ms_step * 1e-3) / 1e9
     line = {
@@ -427,7 +437,8 @@ def main():
         "bwd_tflops": 2.5 * flops_fwd(*shape, ks) / ((ms_dq + ms_dkdv) * 1e-3) / 1e12,
         "tensor_roofline_frac": fl_step / (ms_step * 1e-3) / 1e12 / tensor_peak if tensor_peak else None,
         "roofline": {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": ach / hbm_peak, "traffic": None, "peak_source": peak_kind,
+                     "frac": ach / hbm_peak, "traffic": traffic,
+                     "traffic_source": NCU_TRAFFIC_SOURCE if traffic else None, "peak_source": peak_kind,
                      "algorithmic_bytes_per_launch": dom_bytes},
         "roofline_step": {"bound": "hbm", "achieved": step_ach, "peak": hbm_peak, "unit": "GB/s",
                           "frac": step_ach / hbm_peak, "algorithmic_bytes": ab["step"]},
