@@ -352,7 +352,7 @@ int na2d_check(int device, void* stream) {
 long long na2d_launch_count(void) { return g_launches.load(); }
 
 #ifdef NA2D_TRACE
-// Development aid: copies the trace of the forward kernel's CTA 0 to the host and resets it.
+// Development aid: copies the trace of CTA 0 of the last kernels to the host and clears it.
 int na2d_debug_trace(unsigned long long* out, int max_entries) {
     unsigned int n = 0;
     cudaDeviceSynchronize();
@@ -360,8 +360,8 @@ int na2d_debug_trace(unsigned long long* out, int max_entries) {
     if ((int)n > max_entries) n = max_entries;
     if (n > 8192) n = 8192;
     cudaMemcpyFromSymbol(out, na2d_tc::g_trace, n * sizeof(unsigned long long));
-    unsigned int zero = 0;
-    cudaMemcpyToSymbol(na2d_tc::g_trace_n, &zero, sizeof(zero));
+    void* arr = nullptr;
+    if (cudaGetSymbolAddress(&arr, na2d_tc::g_trace) == cudaSuccess) cudaMemset(arr, 0, sizeof(na2d_tc::g_trace));
     return (int)n;
 }
 #endif

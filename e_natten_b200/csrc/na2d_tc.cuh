@@ -39,10 +39,12 @@ constexpr float kLn2 = 0.6931471805599453f;
 // tensor-memory columns the kernel can spare for the S-shaped accumulators.
 // EXTRA_W widens the box (dK/dV: the inverse neighbourhood of a key tile whose first column is
 // below ks starts at column 0 and is up to ks/2 columns wider than TW + ks - 1).
-template <int D, int KS, int NMAX = 256, int EXTRA_W = 0>
+// W_SPLIT cuts the box into that many column strips, each walked as a chunk of its own (dK/dV).
+template <int D, int KS, int NMAX = 256, int EXTRA_W = 0, int W_SPLIT = 1>
 struct Cfg {
     static constexpr int HH = TH + KS - 1;                 // halo box rows
-    static constexpr int HW = TW + KS - 1 + EXTRA_W;       // halo box columns
+    static constexpr int HW = (TW + KS - 1 + EXTRA_W) / W_SPLIT;   // halo box (or strip) columns
+    static_assert((TW + KS - 1 + EXTRA_W) % W_SPLIT == 0, "strips must tile the box");
     static constexpr int RC_MAX = NMAX / HW;
     static constexpr int NCH = (HH + RC_MAX - 1) / RC_MAX; // key chunks per tile
     static constexpr int RC = (HH + NCH - 1) / NCH;        // box rows per chunk
@@ -104,6 +106,46 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// Output rows leave through TMA: a thread that wrote its own 16-byte pieces straight to global
+// memory would touch 32 different 128-byte lines per warp instruction.  Each softmax warp owns a
+// staging buffer of 32 pixels (32 / TW tile rows x TW columns) x OUT_RW channels, laid out as the
+// tensor map's swizzle wants it, and hands it to one tiled store per OUT_RW channels.
+template <int DH> struct OutStage {
+    static constexpr int RW = DH < 32 ? DH : 32;        // channels per store
+    static constexpr int ROWB = RW * 2;                 // 32 or 64 bytes per pixel
+    static constexpr int BYTES = 32 * ROWB;             // per warp
+    static constexpr int ROUNDS = DH / RW;
+    static_assert(RW == 16 || RW == 32, "staging row is 32 or 64 bytes");
+};
+
+// Stores columns [0, DH) held as fp32 bit patterns in `v` (scaled by `scale`) as 16-bit channels
+// [ch0, ch0 + DH) of the warp's 32 pixels, whose first tile row is image row h0 and first column w0.
+template <typename DT, int DH>
+__device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint8_t* stage, const uint32_t (&v)[DH],
+                                                float scale, int ch0, int w0, int h0, int bn, int lane) {
+    using S = OutStage<DH>;
+    const uint32_t row = smem_u32(stage) + lane * S::ROWB;
+    const int sw = S::ROWB == 64 ? ((lane >> 1) & 3) : ((lane >> 2) & 1);
+#pragma unroll
+    for (int r = 0; r < S::ROUNDS; ++r) {
+        uint32_t w[S::RW / 2];
+#pragma unroll
+        for (int e = 0; e < S::RW / 2; ++e)
+            w[e] = pack2<DT>(__uint_as_float(v[r * S::RW + 2 * e]) * scale, __uint_as_float(v[r * S::RW + 2 * e + 1]) * scale);
+        if (lane == 0) bulk_wait_read<0>();             // the previous store has read the buffer
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < S::ROWB / 16; ++c)
+            st_shared_v4(row + ((c ^ sw) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_4d(map, smem_u32(stage), ch0 + r * S::RW, w0, h0, bn);
+            bulk_commit();
+        }
+    }
+}
+
 // Writes 16 consecutive 16-bit values (packed in pairs) of row `row` of the same operand layout,
 // at columns [16*block16, 16*block16 + 16).
 __device__ __forceinline__ void store_operand_block16(uint32_t base, int slab_bytes, int row, int block16,
@@ -154,17 +196,19 @@ inline EncodeTiledFn encode_fn() {
 
 // Tensor map over a dense (BN, rows, W, C) tensor of 16-bit elements; the box is
 // (min(C, 64) channels) x box_w x box_h x 1, swizzled so that one box row is one swizzle span.
+// box_c = 0 takes min(C, 64) channels; the output maps of the epilogue pass 16 or 32.
 inline int make_map(CUtensorMap* map, const void* base, int dtype, long long BN, int rows, int W, int C,
-                    int box_w, int box_h) {
+                    int box_w, int box_h, int box_c = 0) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return NA2D_ERR_CUDA;
-    const int slab_c = C < 64 ? C : 64;
+    const int slab_c = box_c > 0 ? box_c : (C < 64 ? C : 64);
     cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)rows, (cuuint64_t)BN};
     cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)rows * W * C * 2};
     cuuint32_t box[4] = {(cuuint32_t)slab_c, (cuuint32_t)box_w, (cuuint32_t)box_h, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUtensorMapDataType dt = dtype == NA2D_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const CUtensorMapSwizzle sw = slab_c * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    const CUtensorMapSwizzle sw = slab_c * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : (slab_c * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) last_driver_result() = (int)r;

@@ -16,14 +16,22 @@
 
 namespace na2d_tc {
 
+// The query box of a key tile is walked in chunks of at most 128 queries.  Where a half-width
+// strip of the box holds all of its rows (kernel sizes 3 and 5) the box is cut into a left and a
+// right strip: every warp's keys are then seen from the same number of queries in each chunk,
+// whereas row-wise chunks leave the warps of one half of the tile idle in each chunk (the two
+// warps that share a tensor-memory lane quarter also share an SM sub-partition).
+constexpr int dkv_w_split(int ks) { return 128 / ((TW + ks - 1) / 2) >= TH + ks - 1 ? 2 : 1; }
+
 template <int D, int KS, bool SPLIT>
-struct DkvCfg : Cfg<D, KS, 128> {
-    using B = Cfg<D, KS, 128>;
+struct DkvCfg : Cfg<D, KS, 128, 0, dkv_w_split(KS)> {
+    using B = Cfg<D, KS, 128, 0, dkv_w_split(KS)>;
     // names of the base read as "queries per chunk" here: NK = queries in a chunk, NKP padded
     static constexpr int TMEM_ST = 0, TMEM_DPT = 128, TMEM_DV = 256, TMEM_DK = 384;
     static constexpr int TMEM_PT = 0, TMEM_RES = 64, TMEM_DST = 128;      // 16-bit operands over S^T / dP^T
     static constexpr int STAGE = 2 * B::KV_BYTES;                          // Q chunk then dO chunk
-    static constexpr int FIXED = 2 * B::Q_BYTES /*K, V tile*/ + 2 * 2 * 128 * 4 /*lse, delta x 2*/ + 256 + 1024;
+    static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;          // output staging of the 8 softmax warps
+    static constexpr int FIXED = 2 * B::Q_BYTES /*K, V tile*/ + OUT_BYTES + 2 * 2 * 128 * 4 /*lse, delta x 2*/ + 256 + 1024;
     static constexpr int NSTQ = (FIXED + 3 * STAGE <= kSmemLimit) ? 3 : ((FIXED + 2 * STAGE <= kSmemLimit) ? 2 : 1);
     static constexpr int SMEM = FIXED + NSTQ * STAGE;
     static constexpr int NB16 = B::NKP / 16;
@@ -35,6 +43,7 @@ template <typename DT, int D, int KS>
 __global__ void __launch_bounds__(384, 1)
 dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
             const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+            const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
             const float* __restrict__ lse, const float* __restrict__ delta,
             DT* __restrict__ d_k, DT* __restrict__ d_v, const Na2dGeom g, const int tiles_r, const int tiles_c,
             const int total_tiles) {
@@ -46,7 +55,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     uint8_t* sK = smem;                               // key tile   [128 x D]
     uint8_t* sV = sK + C::Q_BYTES;                    // value tile [128 x D]
     uint8_t* sQD = sV + C::Q_BYTES;                   // NSTQ x (query chunk, dO chunk), each [NKP x D]
-    float* s_lse = reinterpret_cast<float*>(sQD + NSTQ * C::STAGE);   // [chunk parity][128]  lse * log2(e)
+    uint8_t* sOut = sQD + NSTQ * C::STAGE;            // 8 x output staging (1024-byte aligned)
+    float* s_lse = reinterpret_cast<float*>(sOut + C::OUT_BYTES);     // [chunk parity][128]  lse * log2(e)
     float* s_delta = s_lse + 2 * 128;                                   // [chunk parity][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 2 * 128);
     uint64_t* kv_full = bars + 0;            //       TMA -> MMA
@@ -80,6 +90,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         tma_prefetch_desc(&tm_v);
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_do);
+        tma_prefetch_desc(&tm_dk);
+        tma_prefetch_desc(&tm_dv);
     }
     if (warp == 0) {
         __syncwarp();
@@ -173,8 +185,10 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
             mbar_wait(kv_full, it & 1, abort_flag, kErrLoadWait);
             for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
                 const uint32_t st = n % NSTQ;
+                if (leader) NA2D_TR(2, 0, n);
                 mbar_wait(qd_full + st, (n / NSTQ) & 1, abort_flag, kErrLoadWait);
                 tc_fence_after();
+                if (leader) NA2D_TR(2, 1, n);
                 const uint32_t q_addr = smem_u32(sQD + st * C::STAGE), g_addr = q_addr + C::KV_BYTES;
                 if (leader) {
                     const uint32_t q_lo = smem_desc_lo(q_addr, 16), g_lo = smem_desc_lo(g_addr, 16);
@@ -194,11 +208,13 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     }
                     umma_commit(s_full);
                     if (ch == t.n_ch - 1) umma_commit(kv_empty);       // K and V are only read by the score MMAs
+                    NA2D_TR(2, 2, n);
                 }
                 __syncwarp();
                 mbar_wait(p_full, n & 1, abort_flag, kErrMmaWait);
                 if (ch == 0) mbar_wait(acc_free, (it & 1) ^ 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
+                if (leader) NA2D_TR(2, 3, n);
                 if (leader) {
                     const uint32_t qm_lo = smem_desc_lo(q_addr, C::KV_SLAB), gm_lo = smem_desc_lo(g_addr, C::KV_SLAB);
                     const uint32_t acc = ch > 0;
@@ -218,6 +234,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     }
                     umma_commit(qd_empty + st);
                     if (ch == t.n_ch - 1) umma_commit(acc_full);
+                    NA2D_TR(2, 4, n);
                 }
                 __syncwarp();
             }
@@ -272,6 +289,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 const int rc = ch / t.n_cc, cc = ch - rc * t.n_cc;
                 const int r_off = rc * C::RC, c_off = cc * C::HW;
                 const int par = n & 1;
+                if (tid == 0) NA2D_TR(3, 0, n);
                 // lse * log2(e) and delta of the chunk's queries -> shared memory (zero outside the band)
                 if (ctid < C::NK) {
                     const int br = r_off + ctid / C::HW, qc = t.qb_c0 + c_off + ctid % C::HW;
@@ -295,9 +313,11 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 const int seg_len = chi - cl;
                 const uint32_t seg = seg_len > 0 ? ((1u << seg_len) - 1u) : 0u;
                 bar_sync(5, 256);                                           // lse / delta are in place
+                if (tid == 0) NA2D_TR(3, 1, n);
 
                 mbar_wait(s_full, n & 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
+                if (tid == 0) NA2D_TR(3, 2, n);
                 uint32_t s[NACT][16], dp[NACT][16];
                 uint32_t vmask[NACT];
 #pragma unroll
@@ -324,9 +344,11 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     vmask[a] = (blk < b_hi) ? (m & 0xffffu) : 0u;
                 }
                 tmem_ld_wait();
+                if (tid == 0) NA2D_TR(3, 3, n);
                 // the partner has read its S^T / dP^T blocks too: the 16-bit operands may now be
                 // written over them
                 bar_sync(1 + quarter, 64);
+                if (tid == 0) NA2D_TR(3, 4, n);
 
 #pragma unroll
                 for (int a = 0; a < NACT; ++a) {
@@ -377,40 +399,36 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full);
+                if (tid == 0) NA2D_TR(3, 5, n);
             }
 
-            // ---- epilogue: this half's columns of the dV and dK rows of the thread's key
+            // ---- epilogue: this half's columns of the dV and dK rows of the warp's 32 keys
             mbar_wait(acc_full, it & 1, abort_flag, kErrMmaWait);
             tc_fence_after();
+            if (tid == 0) NA2D_TR(3, 6, n - 1);
+            {
+                uint8_t* stage = sOut + warp * OutStage<DH>::BYTES;
+                const int h0 = t.kr0 + quarter * (32 / TW);
+                uint32_t acc[DH];
 #pragma unroll
-            for (int which = 0; which < 2; ++which) {
-                DT* out = which == 0 ? dv_row : dk_row;
-                const uint32_t col0 = (which == 0 ? C::TMEM_DV : C::TMEM_DK) + half * DH;
+                for (int which = 0; which < 2; ++which) {
+                    const uint32_t col0 = (which == 0 ? C::TMEM_DV : C::TMEM_DK) + half * DH;
 #pragma unroll
-                for (int piece = 0; piece < DH / 16; ++piece) {
-                    uint32_t v[16];
-                    tmem_ld_32x16(tmem_lane + col0 + 16 * piece, v);
+                    for (int piece = 0; piece < DH / 16; ++piece)
+                        tmem_ld_32x16(tmem_lane + col0 + 16 * piece, *reinterpret_cast<uint32_t(*)[16]>(&acc[16 * piece]));
                     tmem_ld_wait();
-                    if (k_valid) {
-#pragma unroll
-                        for (int gI = 0; gI < 2; ++gI) {
-                            uint4 pk;
-                            pk.x = pack2<DT>(__uint_as_float(v[8 * gI + 0]), __uint_as_float(v[8 * gI + 1]));
-                            pk.y = pack2<DT>(__uint_as_float(v[8 * gI + 2]), __uint_as_float(v[8 * gI + 3]));
-                            pk.z = pack2<DT>(__uint_as_float(v[8 * gI + 4]), __uint_as_float(v[8 * gI + 5]));
-                            pk.w = pack2<DT>(__uint_as_float(v[8 * gI + 6]), __uint_as_float(v[8 * gI + 7]));
-                            *reinterpret_cast<uint4*>(out + 16 * piece + 8 * gI) = pk;
-                        }
-                    }
+                    stage_and_store<DT, DH>(which == 0 ? &tm_dv : &tm_dk, stage, acc, 1.f, half * DH, t.kc0, h0, t.bn, lane);
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_free);
+            if (tid == 0) NA2D_TR(3, 7, n - 1);
             ++it;
         }
     }
 
+    if (warp < 8 && lane == 0) bulk_wait<0>();          // the staging buffers have been read, the rows written
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
@@ -423,8 +441,10 @@ template <typename DT, int D, int KS>
 int launch_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
                 const void* d_o, const float* delta, void* d_k, void* d_v, int device, cudaStream_t st, int* launched) {
     using C = DkvCfg<D, KS, IsBf16<DT>::value>;
-    CUtensorMap tk, tv, tq, tg;
+    CUtensorMap tk, tv, tq, tg, tdk, tdv;
     int rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&tdk, d_k, dtype, g.BN, g.Hkv, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
+    if (rc == NA2D_OK) rc = make_map(&tdv, d_v, dtype, g.BN, g.Hkv, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
     if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, TW, TH);
     if (rc == NA2D_OK) rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, C::HW, C::RC);
     if (rc == NA2D_OK) rc = make_map(&tg, d_o, dtype, g.BN, g.Hq, g.W, D, C::HW, C::RC);
@@ -436,7 +456,7 @@ int launch_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, cons
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return NA2D_ERR_CUDA;
     const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 384, C::SMEM, st>>>(tk, tv, tq, tg, lse, delta, (DT*)d_k, (DT*)d_v, g, tiles_r, tiles_c, (int)tiles);
+    kern<<<grid, 384, C::SMEM, st>>>(tk, tv, tq, tg, tdk, tdv, lse, delta, (DT*)d_k, (DT*)d_v, g, tiles_r, tiles_c, (int)tiles);
     *launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }
