@@ -27,7 +27,8 @@ struct DqCfg : Cfg<D, KS, ((TH + KS - 1) * (TW + KS - 1) <= 256 ? 256 : 192)> {
     static constexpr int TMEM_DQ = ONE ? 0 : 384;                      // one chunk: dQ reuses the S columns
     static constexpr int TMEM_DSH = TMEM_DP;                           // dS (head) over dP
     static constexpr int TMEM_RES = ONE ? 384 : 0;                     // dS residual: upper dP half / over S
-    static constexpr int FIXED = 2 * B::Q_BYTES + 2 * 2 * 128 * 4 /*delta exchange*/ + 256 + 1024;
+    static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;       // output staging of the 8 softmax warps
+    static constexpr int FIXED = 2 * B::Q_BYTES + OUT_BYTES + 2 * 2 * 128 * 4 /*delta exchange*/ + 256 + 1024;
     static constexpr int SMEM = FIXED + 2 * B::KV_BYTES;               // one K chunk, one V chunk
     static constexpr int NB16 = (B::NKP + 15) / 16;
     static_assert(SMEM <= kSmemLimit, "dQ kernel shared memory");
@@ -39,7 +40,8 @@ template <typename DT, int D, int KS>
 __global__ void __launch_bounds__(384, 1)
 dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
           const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-          const float* __restrict__ lse, DT* __restrict__ d_q, float* __restrict__ delta,
+          const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse, float* __restrict__ delta,
+          const int want_dq_arg,
           const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
     constexpr bool SPLIT = IsBf16<DT>::value;
     using C = DqCfg<D, KS, SPLIT>;
@@ -50,7 +52,8 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     uint8_t* sDO = sQ + C::Q_BYTES;
     uint8_t* sK = sDO + C::Q_BYTES;                   // key chunk   [NKP x D]
     uint8_t* sV = sK + C::KV_BYTES;                   // value chunk [NKP x D]
-    float* x_sum = reinterpret_cast<float*>(sV + C::KV_BYTES);        // [tile parity][half][row]
+    uint8_t* sOut = sV + C::KV_BYTES;                 // 8 x output staging (1024-byte aligned)
+    float* x_sum = reinterpret_cast<float*>(sOut + C::OUT_BYTES);     // [tile parity][half][row]
     uint64_t* bars = reinterpret_cast<uint64_t*>(x_sum + 2 * 2 * 128);
     uint64_t* q_full = bars + 0;             // TMA -> MMA (Q and dO tile)
     uint64_t* q_empty = bars + 1;            // MMA (commit) -> TMA
@@ -68,7 +71,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const bool want_dq = d_q != nullptr;
+    const bool want_dq = want_dq_arg != 0;
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -88,6 +91,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
         tma_prefetch_desc(&tm_do);
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
+        tma_prefetch_desc(&tm_dq);
     }
     if (warp == 0) {
         __syncwarp();
@@ -378,31 +382,22 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 // ---- epilogue: this half's columns of the thread's dQ row
                 mbar_wait(dq_full, i & 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
-                DT* out = d_q + qi * D + half * DH;
+                uint32_t acc[DH];
 #pragma unroll
-                for (int piece = 0; piece < DH / 16; ++piece) {
-                    uint32_t v[16];
-                    tmem_ld_32x16(tmem_lane + C::TMEM_DQ + half * DH + 16 * piece, v);
-                    tmem_ld_wait();
-                    if (q_valid) {
-#pragma unroll
-                        for (int gI = 0; gI < 2; ++gI) {
-                            uint4 pk;
-                            pk.x = pack2<DT>(__uint_as_float(v[8 * gI + 0]), __uint_as_float(v[8 * gI + 1]));
-                            pk.y = pack2<DT>(__uint_as_float(v[8 * gI + 2]), __uint_as_float(v[8 * gI + 3]));
-                            pk.z = pack2<DT>(__uint_as_float(v[8 * gI + 4]), __uint_as_float(v[8 * gI + 5]));
-                            pk.w = pack2<DT>(__uint_as_float(v[8 * gI + 6]), __uint_as_float(v[8 * gI + 7]));
-                            *reinterpret_cast<uint4*>(out + 16 * piece + 8 * gI) = pk;
-                        }
-                    }
-                }
+                for (int piece = 0; piece < DH / 16; ++piece)
+                    tmem_ld_32x16(tmem_lane + C::TMEM_DQ + half * DH + 16 * piece,
+                                  *reinterpret_cast<uint32_t(*)[16]>(&acc[16 * piece]));
+                tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dq_free);
+                stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0,
+                                        r0 + quarter * (32 / TW), bn, lane);
             }
         }
     }
 
+    if (warp < 8 && lane == 0) bulk_wait<0>();          // the staging buffers have been read, the rows written
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
@@ -415,8 +410,10 @@ template <typename DT, int D, int KS>
 int launch_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
               const void* d_o, void* d_q, float* delta, int device, cudaStream_t st, int* launched) {
     using C = DqCfg<D, KS, IsBf16<DT>::value>;
-    CUtensorMap tq, tg, tk, tv;
+    CUtensorMap tq, tg, tk, tv, tdq;
     int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
+    // without a dQ buffer the kernel only writes delta; the map then points at q and is never used
+    if (rc == NA2D_OK) rc = make_map(&tdq, d_q ? d_q : q, dtype, g.BN, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
     if (rc == NA2D_OK) rc = make_map(&tg, d_o, dtype, g.BN, g.Hq, g.W, D, TW, TH);
     if (rc == NA2D_OK) rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
@@ -428,7 +425,7 @@ int launch_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return NA2D_ERR_CUDA;
     const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 384, C::SMEM, st>>>(tq, tg, tk, tv, lse, (DT*)d_q, delta, g, tiles_r, tiles_c, (int)tiles);
+    kern<<<grid, 384, C::SMEM, st>>>(tq, tg, tk, tv, tdq, lse, delta, d_q != nullptr, g, tiles_r, tiles_c, (int)tiles);
     *launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }

@@ -50,7 +50,8 @@ struct FwdCfg : Cfg<D, KS, 256> {
     static constexpr int K_BYTES = B::NS * K_SLAB;
     static constexpr int V_BYTES = B::KV_BYTES;
     static constexpr int XCHG_BYTES = 4 * 2 * 128 * 4;                  // row max [2][2][128], row sum [2][2][128]
-    static constexpr int FIXED = XCHG_BYTES + 256 /*barriers*/ + 1024 /*alignment*/;
+    static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;         // output staging of the 8 softmax warps
+    static constexpr int FIXED = XCHG_BYTES + OUT_BYTES + 256 /*barriers*/ + 1024 /*alignment*/;
     // Ring depths, given out in the order that pays most: a second V slot first (a V slot is only
     // free after the chunk's last MMA, so its refill is what the next tile would wait for), then a
     // second K slot, then a second Q tile.
@@ -70,7 +71,8 @@ struct FwdCfg : Cfg<D, KS, 256> {
 template <typename DT, int D, int KS>
 __global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-           const __grid_constant__ CUtensorMap tm_v, DT* __restrict__ o, float* __restrict__ lse,
+           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+           float* __restrict__ lse,
            const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
     using C = FwdCfg<D, KS>;
     constexpr int NSTK = C::NSTK, NSTV = C::NSTV, NQ = C::NQ;
@@ -79,7 +81,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     uint8_t* sQ = smem;                                   // NQ x Q tile
     uint8_t* sK = sQ + NQ * C::Q_BYTES;                   // NSTK x K chunk
     uint8_t* sV = sK + NSTK * C::K_BYTES;                 // NSTV x V chunk
-    float* x_max = reinterpret_cast<float*>(sV + NSTV * C::V_BYTES);  // [unit parity][half][row]
+    uint8_t* sOut = sV + NSTV * C::V_BYTES;               // 8 x output staging (1024-byte aligned)
+    float* x_max = reinterpret_cast<float*>(sOut + C::OUT_BYTES);     // [unit parity][half][row]
     float* x_sum = x_max + 2 * 2 * 128;                               // [tile parity][half][row]
     uint64_t* bars = reinterpret_cast<uint64_t*>(x_sum + 2 * 2 * 128);
     uint64_t* q_full = bars;                 // [2]   TMA -> MMA
@@ -119,6 +122,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
+        tma_prefetch_desc(&tm_o);
     }
     if (warp == 0) {
         __syncwarp();
@@ -251,6 +255,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         uint32_t pend_tile = 0;
         float pend_max = 0.f, pend_sum = 1.f;
         size_t pend_qi = 0;
+        int pend_bn = 0, pend_r0 = 0, pend_c0 = 0;
 
         auto epilogue = [&]() {
             const uint32_t ob = pend_tile & 1;
@@ -259,27 +264,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             mbar_wait(o_full + ob, (pend_tile >> 1) & 1, abort_flag, kErrMmaWait);
             tc_fence_after();
             const float inv = 1.f / total;
-            DT* orow = o + pend_qi * D + half * DH;
+            uint32_t acc[DH];
 #pragma unroll
-            for (int piece = 0; piece < DH / 16; ++piece) {
-                uint32_t v[16];
-                tmem_ld_32x16(tmem_lane + C::TMEM_O0 + ob * C::TMEM_OSTRIDE + half * DH + 16 * piece, v);
-                tmem_ld_wait();
-                if (pend_valid) {
-#pragma unroll
-                    for (int gI = 0; gI < 2; ++gI) {
-                        uint4 pk;
-                        pk.x = pack2<DT>(__uint_as_float(v[8 * gI + 0]) * inv, __uint_as_float(v[8 * gI + 1]) * inv);
-                        pk.y = pack2<DT>(__uint_as_float(v[8 * gI + 2]) * inv, __uint_as_float(v[8 * gI + 3]) * inv);
-                        pk.z = pack2<DT>(__uint_as_float(v[8 * gI + 4]) * inv, __uint_as_float(v[8 * gI + 5]) * inv);
-                        pk.w = pack2<DT>(__uint_as_float(v[8 * gI + 6]) * inv, __uint_as_float(v[8 * gI + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + 16 * piece + 8 * gI) = pk;
-                    }
-                }
-            }
+            for (int piece = 0; piece < DH / 16; ++piece)
+                tmem_ld_32x16(tmem_lane + C::TMEM_O0 + ob * C::TMEM_OSTRIDE + half * DH + 16 * piece,
+                              *reinterpret_cast<uint32_t(*)[16]>(&acc[16 * piece]));
+            tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(o_free + ob);
+            if (lane == 0) mbar_arrive(o_free + ob);                         // O is in registers
+            stage_and_store<DT, DH>(&tm_o, sOut + warp * OutStage<DH>::BYTES, acc, inv, half * DH, pend_c0,
+                                    pend_r0 + quarter * (32 / TW), pend_bn, lane);
             if (pend_valid && half == 0) lse[pend_qi] = (pend_max + log2f(total)) * kLn2;
             pend = false;
         };
@@ -441,12 +436,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             x_sum[((i & 1) * 2 + half) * 128 + row] = run_sum;
             pend = true;
             pend_tile = (uint32_t)i;
+            pend_bn = bn;
+            pend_r0 = r0;
+            pend_c0 = c0;
             pend_valid = q_valid;
             pend_max = run_max;
             pend_sum = run_sum;
             pend_qi = (static_cast<size_t>(bn) * g.Hq + qr) * g.W + qc;
         }
         if (pend) epilogue();
+        if (lane == 0) bulk_wait<0>();      // the staging buffer has been read, the rows written
     }
 
     tc_fence_before();
@@ -461,8 +460,9 @@ template <typename DT, int D, int KS>
 int launch_forward(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
                    int device, cudaStream_t st, int* launched) {
     using C = FwdCfg<D, KS>;
-    CUtensorMap tq, tk, tv;
+    CUtensorMap tq, tk, tv, to;
     int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&to, o, dtype, g.BN, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
     if (rc == NA2D_OK) rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc != NA2D_OK) return rc;
@@ -473,7 +473,7 @@ int launch_forward(const Na2dGeom& g, int dtype, const void* q, const void* k, c
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return NA2D_ERR_CUDA;
     const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 384, C::SMEM, st>>>(tq, tk, tv, (DT*)o, lse, g, tiles_r, tiles_c, (int)tiles);
+    kern<<<grid, 384, C::SMEM, st>>>(tq, tk, tv, to, lse, g, tiles_r, tiles_c, (int)tiles);
     *launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }
