@@ -171,6 +171,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
             mbar_wait(q_full, i & 1, abort_flag, kErrLoadWait);
             for (int u = 0; u < units_run; ++u, ++n) {
                 const bool forms_ds = want_dq && (C::ONE || u >= NCH);
+                if (leader) NA2D_TR(2, 0, n);
                 mbar_wait(k_full, n & 1, abort_flag, kErrLoadWait);
                 mbar_wait(v_full, n & 1, abort_flag, kErrLoadWait);
                 // the accumulators the score MMAs overwrite must have been read
@@ -187,6 +188,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 }
                 tc_fence_after();
                 if (leader) {
+                    NA2D_TR(2, 1, n);
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         constexpr int kPerSlab = C::SLAB_C / 16;
@@ -205,6 +207,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                     umma_commit(v_empty);
                     if (!forms_ds) umma_commit(k_empty);
                     if (u == units_run - 1) umma_commit(q_empty);     // last score MMAs of the tile
+                    NA2D_TR(2, 2, n);
                 }
                 __syncwarp();
                 if (!forms_ds) { ++n_free; continue; }
@@ -213,6 +216,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 if (!C::ONE && u == NCH && i > 0) mbar_wait(dq_free, (i & 1) ^ 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
                 if (leader) {
+                    NA2D_TR(2, 3, n);
                     const uint32_t acc = (!C::ONE && u > NCH) ? 1u : 0u;
 #pragma unroll
                     for (int kk = 0; kk < C::NKP / 16; ++kk)
@@ -226,6 +230,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                     }
                     umma_commit(k_empty);
                     if (u == units_run - 1) umma_commit(dq_full);
+                    NA2D_TR(2, 4, n);
                 }
                 __syncwarp();
             }
@@ -271,8 +276,10 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 const int b_hi = (max(j_hi, 0) + 15) >> 4;
                 const int bi_lo = ((j_lo >> 4) - half + 1) >> 1;
 
+                if (tid == 0) NA2D_TR(3, 0, n);
                 mbar_wait(s_full, n & 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
+                if (tid == 0) NA2D_TR(3, 1, n);
                 uint32_t s[NACT][16], dp[NACT][16];
                 uint32_t vmask[NACT];
 #pragma unroll
@@ -298,6 +305,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                     vmask[a] = (blk < b_hi) ? (m & 0xffffu) : 0u;
                 }
                 tmem_ld_wait();
+                if (tid == 0) NA2D_TR(3, 2, n);
 
                 // p = exp(s - lse) in place of s; this half's part of delta
                 float d0 = 0.f, d1 = 0.f;
@@ -335,6 +343,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                     bar_sync(1 + quarter, 64);
                 }
 
+                if (tid == 0) NA2D_TR(3, 3, n);
                 if (!forms_ds) {
                     tc_fence_before();
                     __syncwarp();
@@ -376,12 +385,14 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full);
+                if (tid == 0) NA2D_TR(3, 4, n);
             }
 
             if (want_dq) {
                 // ---- epilogue: this half's columns of the thread's dQ row
                 mbar_wait(dq_full, i & 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
+                if (tid == 0) NA2D_TR(3, 5, n - 1);
                 uint32_t acc[DH];
 #pragma unroll
                 for (int piece = 0; piece < DH / 16; ++piece)
@@ -391,8 +402,10 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dq_free);
+                if (tid == 0) NA2D_TR(3, 6, n - 1);
                 stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0,
                                         r0 + quarter * (32 / TW), bn, lane);
+                if (tid == 0) NA2D_TR(3, 7, n - 1);
             }
         }
     }

@@ -3,44 +3,70 @@
 // One CTA per SM walks key tiles (TH x TW keys, row r of every MMA = key r = tensor-memory lane
 // r).  The queries that can see a tile form a box (the union of the keys' inverse
 // neighbourhoods, clipped to the local query band), walked in chunks of RC rows x HW columns
-// (at most 128 queries):
+// (at most 64 queries):
 //     S^T = K Q_c^T,  dP^T = V dO_c^T                      (tensor memory, fp32)
 //     P^T = exp(S^T - lse),  dS^T = P^T (dP^T - delta)     (softmax warps, registers)
 //     dV += P^T dO_c,  dK += dS^T Q_c                      (P^T, dS^T read from tensor memory)
 // P^T and dS^T are written back over S^T / dP^T as packed 16-bit pairs; on the bf16 path dS^T
 // is written as head + residual (two MMAs), because one bf16 keeps too few bits for dK.
-// Twelve warps: 0-7 softmax (warps w and w+4 share 32 keys and split the 16-column blocks),
-// 8 TMA producer (K, V tile; ring of Q / dO chunks), 9 MMA issue, 10-11 idle (register donors).
-// dK and dV accumulate in tensor memory over all chunks of a tile; no atomics.
+//
+// Tensor memory holds two chunk stages (S^T, dP^T of 64 columns each) next to the dV and dK
+// accumulators, so the score MMAs of one chunk run while the softmax warps work on the previous
+// one.  Sixteen warps: 0-3 and 4-7 are two softmax groups that take alternate chunks (a warp owns
+// the 32 keys of its lane quarter), 8 TMA producer (K, V tile; ring of Q / dO chunks), 9 MMA
+// issue, 10-11 idle (register donors), 12-15 epilogue (dV, dK rows -> staging -> TMA store), which
+// overlaps the next tile.  dK and dV accumulate in tensor memory over all chunks of a tile; no
+// atomics.
 #pragma once
 
 namespace na2d_tc {
 
-// The query box of a key tile is walked in chunks of at most 128 queries.  Where a half-width
-// strip of the box holds all of its rows (kernel sizes 3 and 5) the box is cut into a left and a
-// right strip: every warp's keys are then seen from the same number of queries in each chunk,
-// whereas row-wise chunks leave the warps of one half of the tile idle in each chunk (the two
-// warps that share a tensor-memory lane quarter also share an SM sub-partition).
-constexpr int dkv_w_split(int ks) { return 128 / ((TW + ks - 1) / 2) >= TH + ks - 1 ? 2 : 1; }
+// Chunks of an interior tile's query box when the box is cut into `split` column strips.
+constexpr int dkv_chunks(int ks, int split) {
+    const int bw = TW + ks - 1, hh = TH + ks - 1;
+    if (bw % split != 0 || 64 / (bw / split) == 0) return 1 << 20;
+    const int rc_max = 64 / (bw / split);
+    return (hh + rc_max - 1) / rc_max * split;
+}
+// Fewest chunks wins; on a tie the narrower strips, which spread the work evenly over the lane
+// quarters (a key row group sees the same number of queries in every strip).
+constexpr int dkv_w_split(int ks) {
+    const int c1 = dkv_chunks(ks, 1), c2 = dkv_chunks(ks, 2), c4 = dkv_chunks(ks, 4);
+    return (c4 <= c2 && c4 <= c1) ? 4 : (c2 <= c1 ? 2 : 1);
+}
+
+constexpr unsigned long long row_repeat(int hw, int rc) {
+    unsigned long long m = 0;
+    for (int r = 0; r < rc; ++r) m |= 1ull << (r * hw);
+    return m;
+}
+
+// Registers per thread after re-balancing (512 threads are launched with 128 each).
+constexpr int kDkvRegsLaunch = 128, kDkvRegsSoftmax = 176, kDkvRegsCtl = 72, kDkvRegsEpi = 88;
+static_assert((kDkvRegsSoftmax - kDkvRegsLaunch) * 8 <= (kDkvRegsLaunch - kDkvRegsCtl) * 4 + (kDkvRegsLaunch - kDkvRegsEpi) * 4,
+              "setmaxnreg.inc would wait for ever");
 
 template <int D, int KS, bool SPLIT>
-struct DkvCfg : Cfg<D, KS, 128, 0, dkv_w_split(KS)> {
-    using B = Cfg<D, KS, 128, 0, dkv_w_split(KS)>;
+struct DkvCfg : Cfg<D, KS, 64, 0, dkv_w_split(KS)> {
+    using B = Cfg<D, KS, 64, 0, dkv_w_split(KS)>;
     // names of the base read as "queries per chunk" here: NK = queries in a chunk, NKP padded
-    static constexpr int TMEM_ST = 0, TMEM_DPT = 128, TMEM_DV = 256, TMEM_DK = 384;
-    static constexpr int TMEM_PT = 0, TMEM_RES = 64, TMEM_DST = 128;      // 16-bit operands over S^T / dP^T
+    static constexpr int TMEM_STAGE = 128;                                 // columns per chunk stage
+    static constexpr int TMEM_ST = 0, TMEM_DPT = 64, TMEM_DV = 256, TMEM_DK = 384;
+    static constexpr int TMEM_PT = 0, TMEM_DST = 32, TMEM_RES = 64;       // 16-bit operands over S^T / dP^T
     static constexpr int STAGE = 2 * B::KV_BYTES;                          // Q chunk then dO chunk
-    static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;          // output staging of the 8 softmax warps
-    static constexpr int FIXED = 2 * B::Q_BYTES /*K, V tile*/ + OUT_BYTES + 2 * 2 * 128 * 4 /*lse, delta x 2*/ + 256 + 1024;
-    static constexpr int NSTQ = (FIXED + 3 * STAGE <= kSmemLimit) ? 3 : ((FIXED + 2 * STAGE <= kSmemLimit) ? 2 : 1);
+    static constexpr int OUT_BYTES = 4 * OutStage<32>::BYTES;              // staging of the 4 epilogue warps
+    static constexpr int XCHG_BYTES = 2 * 2 * 2 * 64 * 4;                  // [group][parity]{lse, delta}[64]
+    static constexpr int FIXED = 2 * B::Q_BYTES /*K, V tile*/ + OUT_BYTES + XCHG_BYTES + 256 + 1024;
+    static constexpr int NSTQ = (FIXED + 4 * STAGE <= kSmemLimit) ? 4 : 3;
     static constexpr int SMEM = FIXED + NSTQ * STAGE;
-    static constexpr int NB16 = B::NKP / 16;
+    static constexpr int NB8 = B::NKP / 8;
+    static constexpr unsigned long long ROW_REP = row_repeat(B::HW, B::RC);
     static_assert(SMEM <= kSmemLimit, "dK/dV kernel shared memory");
-    static_assert(B::NKP <= 128 && D <= 128, "tensor memory layout");
+    static_assert(B::NKP <= 64 && D <= 128 && D % 32 == 0, "tensor memory layout");
 };
 
 template <typename DT, int D, int KS>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(512, 1)
 dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
             const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
             const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
@@ -55,19 +81,18 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     uint8_t* sK = smem;                               // key tile   [128 x D]
     uint8_t* sV = sK + C::Q_BYTES;                    // value tile [128 x D]
     uint8_t* sQD = sV + C::Q_BYTES;                   // NSTQ x (query chunk, dO chunk), each [NKP x D]
-    uint8_t* sOut = sQD + NSTQ * C::STAGE;            // 8 x output staging (1024-byte aligned)
-    float* s_lse = reinterpret_cast<float*>(sOut + C::OUT_BYTES);     // [chunk parity][128]  lse * log2(e)
-    float* s_delta = s_lse + 2 * 128;                                   // [chunk parity][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 2 * 128);
+    uint8_t* sOut = sQD + NSTQ * C::STAGE;            // 4 x output staging (1024-byte aligned)
+    float* s_x = reinterpret_cast<float*>(sOut + C::OUT_BYTES);   // [group][parity]{lse * log2(e), delta}[64]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_x + C::XCHG_BYTES / 4);
     uint64_t* kv_full = bars + 0;            //       TMA -> MMA
     uint64_t* kv_empty = bars + 1;           //       MMA (commit) -> TMA
-    uint64_t* s_full = bars + 2;             //       MMA (commit) -> softmax
-    uint64_t* p_full = bars + 3;             //       softmax -> MMA
-    uint64_t* acc_full = bars + 4;           //       MMA (commit) -> softmax (epilogue)
-    uint64_t* acc_free = bars + 5;           //       softmax -> MMA
-    uint64_t* qd_full = bars + 6;            // [3]   TMA -> MMA
-    uint64_t* qd_empty = bars + 9;           // [3]   MMA (commit) -> TMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint64_t* acc_full = bars + 2;           //       MMA (commit) -> epilogue
+    uint64_t* acc_free = bars + 3;           //       epilogue -> MMA
+    uint64_t* s_full = bars + 4;             // [2]   MMA (commit) -> softmax group
+    uint64_t* p_full = bars + 6;             // [2]   softmax group -> MMA
+    uint64_t* qd_full = bars + 8;            // [4]   TMA -> MMA
+    uint64_t* qd_empty = bars + 12;          // [4]   MMA (commit) -> TMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -77,11 +102,13 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         *abort_flag = 0;
         mbar_init(kv_full, 1);
         mbar_init(kv_empty, 1);
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 8);
         mbar_init(acc_full, 1);
-        mbar_init(acc_free, 8);
-        for (int i = 0; i < 3; ++i) {
+        mbar_init(acc_free, 4);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_full + i, 1);
+            mbar_init(p_full + i, 4);
+        }
+        for (int i = 0; i < 4; ++i) {
             mbar_init(qd_full + i, 1);
             mbar_init(qd_empty + i, 1);
         }
@@ -102,7 +129,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     // TMA never writes: zero them once.
     if constexpr (C::NKP > C::NK) {
         constexpr int pad16 = (C::NKP - C::NK) * C::ROWB / 16;
-        for (int i = tid; i < NSTQ * 2 * C::NS * pad16; i += 384) {
+        for (int i = tid; i < NSTQ * 2 * C::NS * pad16; i += 512) {
             const int which = i / pad16, off = i - which * pad16;          // which = (stage * 2 + q/dO) * NS + slab
             const int slab = which % C::NS, buf = which / C::NS;
             uint8_t* base = sQD + (buf >> 1) * C::STAGE + (buf & 1) * C::KV_BYTES + slab * C::KV_SLAB;
@@ -133,14 +160,14 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         t.q_local_r0 = t.qb_r0 - g.q_row0;
         t.qb_c0 = na2d_bws(t.kc0, KS);
         const int n_cols = na2d_bwe(min(t.kc0 + TW, g.W) - 1, g.W, KS) - t.qb_c0;
-        t.n_cc = (n_cols + C::HW - 1) / C::HW;           // 1 inside the image, 2 where both borders stretch the box
+        t.n_cc = (n_cols + C::HW - 1) / C::HW;           // strips; more where both borders stretch the box
         t.n_ch = ((t.n_rows + C::RC - 1) / C::RC) * t.n_cc;
         return t;
     };
 
     if (warp == 8) {
         // ------------------------------------------------------------------ producer
-        reg_dec<kRegsDonor>();
+        reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
             uint32_t n = 0, it = 0;                     // chunk counter, non-empty tile counter
             for (int i = 0; i < n_my; ++i) {
@@ -172,110 +199,194 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
-        reg_dec<kRegsDonor>();
-        const bool leader = lane == 0;
-        constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
-        constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
-        constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
-        const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16), v_lo = smem_desc_lo(smem_u32(sV), 16);
-        uint32_t n = 0, it = 0;
-        for (int i = 0; i < n_my; ++i) {
-            const TileGeo t = tile_geo(i);
-            if (t.n_ch == 0) continue;
-            mbar_wait(kv_full, it & 1, abort_flag, kErrLoadWait);
-            for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
-                const uint32_t st = n % NSTQ;
-                if (leader) NA2D_TR(2, 0, n);
-                mbar_wait(qd_full + st, (n / NSTQ) & 1, abort_flag, kErrLoadWait);
+        // Per chunk n two batches are issued: the score MMAs of chunk n into stage n & 1 and the
+        // output MMAs of chunk n - 1 out of the other stage.  Neither depends on the other, so
+        // whichever has its inputs first goes first; the score MMAs of chunk n + 1 reuse the stage
+        // of chunk n - 1 and are issued after both.  The whole warp walks this code with uniform
+        // control flow; one elected lane executes the MMA and commit instructions.
+        reg_dec<kDkvRegsCtl>();
+        {
+            const uint32_t leader = lane == 0 ? 1u : 0u;
+            constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
+            constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
+            constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
+            const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16), v_lo = smem_desc_lo(smem_u32(sV), 16);
+            const uint32_t qd_base = smem_u32(sQD);
+
+            auto issue_scores = [&](uint32_t n, bool last_of_tile) {
+                const uint32_t q_addr = qd_base + (n % NSTQ) * C::STAGE, g_addr = q_addr + C::KV_BYTES;
+                const uint32_t q_lo = smem_desc_lo(q_addr, 16), g_lo = smem_desc_lo(g_addr, 16);
+                const uint32_t tm = tmem_base + (n & 1) * C::TMEM_STAGE;
                 tc_fence_after();
-                if (leader) NA2D_TR(2, 1, n);
-                const uint32_t q_addr = smem_u32(sQD + st * C::STAGE), g_addr = q_addr + C::KV_BYTES;
-                if (leader) {
-                    const uint32_t q_lo = smem_desc_lo(q_addr, 16), g_lo = smem_desc_lo(g_addr, 16);
+                if (elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         constexpr int kPerSlab = C::SLAB_C / 16;
                         const int slab = kk / kPerSlab, in_slab = kk % kPerSlab;
-                        umma_ss(tmem_base + C::TMEM_ST, desc64(hi, k_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
+                        umma_ss(tm + C::TMEM_ST, desc64(hi, k_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
                                 desc64(hi, q_lo + ((slab * C::KV_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
-                    }
-#pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        constexpr int kPerSlab = C::SLAB_C / 16;
-                        const int slab = kk / kPerSlab, in_slab = kk % kPerSlab;
-                        umma_ss(tmem_base + C::TMEM_DPT, desc64(hi, v_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
+                        umma_ss(tm + C::TMEM_DPT, desc64(hi, v_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
                                 desc64(hi, g_lo + ((slab * C::KV_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
                     }
-                    umma_commit(s_full);
-                    if (ch == t.n_ch - 1) umma_commit(kv_empty);       // K and V are only read by the score MMAs
+                    umma_commit(s_full + (n & 1));
+                    if (last_of_tile) umma_commit(kv_empty);           // K and V are only read by the score MMAs
                     NA2D_TR(2, 2, n);
                 }
                 __syncwarp();
-                mbar_wait(p_full, n & 1, abort_flag, kErrMmaWait);
-                if (ch == 0) mbar_wait(acc_free, (it & 1) ^ 1, abort_flag, kErrMmaWait);
+            };
+            auto issue_outputs = [&](uint32_t n, bool first_of_tile, bool last_of_tile) {
+                const uint32_t q_addr = qd_base + (n % NSTQ) * C::STAGE, g_addr = q_addr + C::KV_BYTES;
+                const uint32_t qm_lo = smem_desc_lo(q_addr, C::KV_SLAB), gm_lo = smem_desc_lo(g_addr, C::KV_SLAB);
+                const uint32_t tm = tmem_base + (n & 1) * C::TMEM_STAGE;
+                const uint32_t acc = first_of_tile ? 0u : 1u;
                 tc_fence_after();
-                if (leader) NA2D_TR(2, 3, n);
-                if (leader) {
-                    const uint32_t qm_lo = smem_desc_lo(q_addr, C::KV_SLAB), gm_lo = smem_desc_lo(g_addr, C::KV_SLAB);
-                    const uint32_t acc = ch > 0;
+                if (elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < C::NKP / 16; ++kk)
-                        umma_ts(tmem_base + C::TMEM_DV, tmem_base + C::TMEM_PT + 8 * kk,
-                                desc64(hi, gm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
-#pragma unroll
-                    for (int kk = 0; kk < C::NKP / 16; ++kk)
-                        umma_ts(tmem_base + C::TMEM_DK, tmem_base + C::TMEM_DST + 8 * kk,
+                    for (int kk = 0; kk < C::NKP / 16; ++kk) {
+                        umma_ts(tmem_base + C::TMEM_DK, tm + C::TMEM_DST + 8 * kk,
                                 desc64(hi, qm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
+                        umma_ts(tmem_base + C::TMEM_DV, tm + C::TMEM_PT + 8 * kk,
+                                desc64(hi, gm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
+                    }
                     if (SPLIT) {
 #pragma unroll
                         for (int kk = 0; kk < C::NKP / 16; ++kk)
-                            umma_ts(tmem_base + C::TMEM_DK, tmem_base + C::TMEM_RES + 8 * kk,
+                            umma_ts(tmem_base + C::TMEM_DK, tm + C::TMEM_RES + 8 * kk,
                                     desc64(hi, qm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, 1u);
                     }
-                    umma_commit(qd_empty + st);
-                    if (ch == t.n_ch - 1) umma_commit(acc_full);
+                    umma_commit(qd_empty + (n % NSTQ));
+                    if (last_of_tile) umma_commit(acc_full);
                     NA2D_TR(2, 4, n);
                 }
                 __syncwarp();
-            }
-            ++it;
-        }
-    } else if (warp >= 10) {
-        reg_dec<kRegsDonor>();
-    } else {
-        // ------------------------------------------------------------------ softmax warps
-        reg_inc<kRegsSoftmax>();
-        const int quarter = warp & 3, half = warp >> 2;
-        const int row = quarter * 32 + lane;                 // key of the tile = tensor-memory lane
-        const int ctid = warp * 32 + lane;                   // 0..255 among the softmax warps
-        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        constexpr int DH = D / 2;                            // output columns stored by this half
-        constexpr int NBH = (C::NB16 + 1) / 2;               // own blocks at most
-        // a warp's 32 / TW key rows are seen from at most that many + 2 ks - 2 query rows
-        constexpr int kRows = (32 / TW - 1 + 2 * KS - 1) < C::RC ? (32 / TW - 1 + 2 * KS - 1) : C::RC;
-        constexpr int kBlocks = (kRows * C::HW - 1) / 16 + 2;
-        constexpr int NACT = (kBlocks + 1) / 2 < NBH ? (kBlocks + 1) / 2 : NBH;
-        constexpr int NR = (16 + C::HW - 2) / C::HW + 1;     // chunk rows a 16-column block can touch
+            };
 
-        uint32_t n = 0, it = 0;
+            uint32_t n = 0, it = 0;
+            bool have_prev = false, prev_first = false, prev_last = false;
+            uint32_t prev_it = 0;
+            bool gave_up = false;
+            // Issues the score MMAs of chunk n (when `scores`) and the output MMAs of chunk n - 1
+            // (when there is one), in the order their inputs arrive.  Every lane tests the
+            // barriers; a batch goes out when all lanes have seen its inputs.
+            auto step = [&](bool scores, bool first, bool last) {
+                bool done_x = !scores, done_y = !have_prev;
+                const uint32_t limit = (*abort_flag != 0 || gave_up) ? kSpinLimitAborted : kSpinLimit;
+                uint32_t spins = 0;
+                if (leader) NA2D_TR(2, 0, n);
+                while (!(done_x && done_y)) {
+                    if (!done_x) {
+                        const bool ready = mbar_test(qd_full + n % NSTQ, (n / NSTQ) & 1) && (!first || mbar_test(kv_full, it & 1));
+                        if (__all_sync(0xffffffffu, ready)) {
+                            issue_scores(n, last);
+                            done_x = true;
+                        }
+                    }
+                    if (!done_y) {
+                        const bool ready = mbar_test(p_full + ((n - 1) & 1), ((n - 1) >> 1) & 1) &&
+                                           (!prev_first || mbar_test(acc_free, (prev_it & 1) ^ 1));
+                        if (__all_sync(0xffffffffu, ready)) {
+                            issue_outputs(n - 1, prev_first, prev_last);
+                            done_y = true;
+                        }
+                    }
+                    if (++spins > limit) {                              // give up: later waits are short
+                        if (leader) {
+                            *abort_flag = 1;
+                            atomicOr(&g_error_word, kErrMmaWait);
+                        }
+                        gave_up = true;
+                        break;
+                    }
+                    if (spins > 4096) __nanosleep(32);
+                }
+            };
+            for (int i = 0; i < n_my; ++i) {
+                const TileGeo t = tile_geo(i);
+                if (t.n_ch == 0) continue;
+                for (int ch = 0; ch < t.n_ch; ++ch) {
+                    const bool first = ch == 0, last = ch == t.n_ch - 1;
+                    step(true, first, last);
+                    have_prev = true;
+                    prev_first = first;
+                    prev_last = last;
+                    prev_it = it;
+                    ++n;
+                }
+                ++it;
+            }
+            step(false, false, false);                                  // output MMAs of the last chunk
+        }
+        __syncwarp();
+    } else if (warp == 10 || warp == 11) {
+        reg_dec<kDkvRegsCtl>();
+    } else if (warp >= 12) {
+        // ------------------------------------------------------------------ epilogue warps
+        reg_dec<kDkvRegsEpi>();
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                 // key of the tile = tensor-memory lane
+        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        uint8_t* stage = sOut + quarter * OutStage<32>::BYTES;
+        constexpr int RPO = D / 32;                          // 32-channel rounds per output
+        uint32_t it = 0;
         for (int i = 0; i < n_my; ++i) {
             const TileGeo t = tile_geo(i);
-            const int kr_raw = t.kr0 + (row / TW), kc_raw = t.kc0 + (row % TW);
-            const bool k_valid = kr_raw < g.Hkv && kc_raw < g.W;
-            const int kr = min(kr_raw, g.Hkv - 1), kc = min(kc_raw, g.W - 1);
-            const size_t ki = (static_cast<size_t>(t.bn) * g.Hkv + kr) * g.W + kc;
-            DT* dv_row = d_v + ki * D + half * DH;
-            DT* dk_row = d_k + ki * D + half * DH;
-            if (t.n_ch == 0) {                               // no local query sees this tile
-                if (k_valid) {
+            if (t.n_ch == 0) {                               // no local query sees this tile: zeros
+                const int kr = t.kr0 + (row / TW), kc = t.kc0 + (row % TW);
+                if (kr < g.Hkv && kc < g.W) {
+                    const size_t ki = (static_cast<size_t>(t.bn) * g.Hkv + kr) * g.W + kc;
 #pragma unroll
-                    for (int c8 = 0; c8 < DH / 8; ++c8) {
-                        *reinterpret_cast<uint4*>(dv_row + 8 * c8) = make_uint4(0u, 0u, 0u, 0u);
-                        *reinterpret_cast<uint4*>(dk_row + 8 * c8) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int c8 = 0; c8 < D / 8; ++c8) {
+                        *reinterpret_cast<uint4*>(d_v + ki * D + 8 * c8) = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4*>(d_k + ki * D + 8 * c8) = make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
                 continue;
             }
+            if (warp == 12 && lane == 0) NA2D_TR(0, 0, it);
+            mbar_wait(acc_full, it & 1, abort_flag, kErrMmaWait);
+            tc_fence_after();
+            if (warp == 12 && lane == 0) NA2D_TR(0, 1, it);
+            const int h0 = t.kr0 + quarter * (32 / TW);
+            // 2 * RPO rounds of 32 columns, the load of the next round in flight while one is stored
+            uint32_t v[2][32];
+            tmem_ld_32x32(tmem_lane + C::TMEM_DV, v[0]);
+#pragma unroll
+            for (int j = 0; j < 2 * RPO; ++j) {
+                tmem_ld_wait();
+                if (j + 1 < 2 * RPO) {
+                    const int which = (j + 1) / RPO, r = (j + 1) % RPO;
+                    tmem_ld_32x32(tmem_lane + (which == 0 ? C::TMEM_DV : C::TMEM_DK) + 32 * r, v[(j + 1) & 1]);
+                } else {                                     // both accumulators are in registers
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_free);
+                    if (warp == 12 && lane == 0) NA2D_TR(0, 2, it);
+                }
+                stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 1.f, 32 * (j % RPO), t.kc0, h0,
+                                        t.bn, lane);
+            }
+            if (warp == 12 && lane == 0) NA2D_TR(0, 3, it);
+            ++it;
+        }
+        if (lane == 0) bulk_wait<0>();                       // the staging buffer has been read, the rows written
+    } else {
+        // ------------------------------------------------------------------ softmax groups
+        reg_inc<kDkvRegsSoftmax>();
+        const int quarter = warp & 3, group = warp >> 2;
+        const int row = quarter * 32 + lane;                 // key of the tile = tensor-memory lane
+        const int gtid = quarter * 32 + lane;                // 0..127 inside the group
+        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + group * C::TMEM_STAGE;
+        // a warp's 32 / TW key rows are seen from at most that many + 2 ks - 2 query rows
+        constexpr int kRows = (32 / TW - 1 + 2 * KS - 1) < C::RC ? (32 / TW - 1 + 2 * KS - 1) : C::RC;
+        constexpr int kBlocks = (kRows * C::HW - 1) / 8 + 2;
+        constexpr int NACT = kBlocks < C::NB8 ? kBlocks : C::NB8;   // 8-column blocks a warp can have in range
+        constexpr unsigned long long kRowRep = C::ROW_REP;          // bit r * HW set for every chunk row r
+
+        uint32_t n = 0;
+        for (int i = 0; i < n_my; ++i) {
+            const TileGeo t = tile_geo(i);
+            if (t.n_ch == 0) continue;
+            const int kr = min(t.kr0 + (row / TW), g.Hkv - 1), kc = min(t.kc0 + (row % TW), g.W - 1);
             // the queries that see this thread's key: box rows [row_lo, row_hi), box columns [col_lo, col_hi)
             const int kg = g.kv_row0 + kr;
             const int row_lo = max(na2d_bws(kg, KS), g.q_row0) - t.qb_r0;
@@ -286,85 +397,83 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
             const int wrow_hi = __shfl_sync(0xffffffffu, row_hi, 31);
 
             for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
+                if ((n & 1u) != (uint32_t)group) continue;  // the other group's chunk
+                const uint32_t k = n >> 1;                  // this group's chunk counter
                 const int rc = ch / t.n_cc, cc = ch - rc * t.n_cc;
                 const int r_off = rc * C::RC, c_off = cc * C::HW;
-                const int par = n & 1;
-                if (tid == 0) NA2D_TR(3, 0, n);
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 0, n);
+                float* x_lse = s_x + ((group * 2 + (k & 1)) * 2) * 64;
+                float* x_delta = x_lse + 64;
                 // lse * log2(e) and delta of the chunk's queries -> shared memory (zero outside the band)
-                if (ctid < C::NK) {
-                    const int br = r_off + ctid / C::HW, qc = t.qb_c0 + c_off + ctid % C::HW;
+                if (gtid < C::NK) {
+                    const int br = r_off + gtid / C::HW, qc = t.qb_c0 + c_off + gtid % C::HW;
                     float l2 = 0.f, dl = 0.f;
                     if (br < t.n_rows && qc < g.W) {
                         const size_t qi = (static_cast<size_t>(t.bn) * g.Hq + (t.q_local_r0 + br)) * g.W + qc;
                         l2 = lse[qi] * kLog2e;
                         dl = delta[qi];
                     }
-                    s_lse[par * 128 + ctid] = l2;
-                    s_delta[par * 128 + ctid] = dl;
+                    x_lse[gtid] = l2;
+                    x_delta[gtid] = dl;
                 }
                 // the warp's keys are seen from chunk rows [ra, rb): its active column range
                 const int ra = max(wrow_lo - r_off, 0), rb = min(wrow_hi - r_off, C::RC);
                 const int j_lo = ra * C::HW;
                 const int j_hi = rb > ra ? min(rb * C::HW, C::NK) : 0;
-                const int b_hi = (j_hi + 15) >> 4;
-                const int bi_lo = j_hi > 0 ? (((j_lo >> 4) - half + 1) >> 1) : 0;
+                const int b_hi = (j_hi + 7) >> 3;
+                const int b_lo = j_hi > 0 ? (j_lo >> 3) : 0;
                 // this thread's column segment inside a chunk row
                 const int cl = max(col_lo - c_off, 0), chi = min(col_hi - c_off, C::HW);
                 const int seg_len = chi - cl;
                 const uint32_t seg = seg_len > 0 ? ((1u << seg_len) - 1u) : 0u;
-                bar_sync(5, 256);                                           // lse / delta are in place
-                if (tid == 0) NA2D_TR(3, 1, n);
+                bar_sync(5 + group, 128);                                   // lse / delta are in place
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 1, n);
 
-                mbar_wait(s_full, n & 1, abort_flag, kErrMmaWait);
+                mbar_wait(s_full + group, k & 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
-                if (tid == 0) NA2D_TR(3, 2, n);
-                uint32_t s[NACT][16], dp[NACT][16];
-                uint32_t vmask[NACT];
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 2, n);
+                uint32_t s[NACT][8], dp[NACT][8];
 #pragma unroll
                 for (int a = 0; a < NACT; ++a) {
-                    const int blk = half + 2 * (bi_lo + a);
+                    const int blk = b_lo + a;
                     if (blk < b_hi) {                                       // warp-uniform
-                        tmem_ld_32x16(tmem_lane + C::TMEM_ST + 16 * blk, s[a]);
-                        tmem_ld_32x16(tmem_lane + C::TMEM_DPT + 16 * blk, dp[a]);
+                        tmem_ld_32x8(tmem_lane + C::TMEM_ST + 8 * blk, s[a]);
+                        tmem_ld_32x8(tmem_lane + C::TMEM_DPT + 8 * blk, dp[a]);
                     }
                 }
+                // validity of the chunk's (at most 64) columns for this thread's key, one bit each:
+                // its column segment repeated in every chunk row, cut to its row range
+                uint32_t vmask[NACT];
+                {
+                    const int ta = max(row_lo - r_off, 0), tb = min(row_hi - r_off, C::RC);
+                    const unsigned long long rows_hi = tb * C::HW >= 64 ? ~0ull : ((1ull << (max(tb, 0) * C::HW)) - 1ull);
+                    const unsigned long long rows_lo = (1ull << (ta * C::HW)) - 1ull;       // ta * HW < 64
+                    const unsigned long long m64 = tb > ta ? (((kRowRep * seg) << cl) & rows_hi & ~rows_lo) : 0ull;
 #pragma unroll
-                for (int a = 0; a < NACT; ++a) {                            // validity masks, loads in flight
-                    const int blk = half + 2 * (bi_lo + a);
-                    const int r_first = (16 * blk) / C::HW;
-                    uint32_t m = 0;
-#pragma unroll
-                    for (int dr = 0; dr < NR; ++dr) {
-                        const int r = r_first + dr;                          // chunk row
-                        const int rel = r * C::HW + cl - 16 * blk;           // segment start relative to the block
-                        const uint32_t bits = rel >= 0 ? (seg << (rel & 31)) : (seg >> ((-rel) & 31));
-                        const bool row_ok = r < C::RC && r_off + r >= row_lo && r_off + r < row_hi;
-                        if (row_ok && rel > -32 && rel < 16) m |= bits;
+                    for (int a = 0; a < NACT; ++a) {
+                        const int blk = b_lo + a;
+                        vmask[a] = (blk < b_hi) ? (static_cast<uint32_t>(m64 >> (8 * blk)) & 0xffu) : 0u;
                     }
-                    vmask[a] = (blk < b_hi) ? (m & 0xffffu) : 0u;
                 }
                 tmem_ld_wait();
-                if (tid == 0) NA2D_TR(3, 3, n);
-                // the partner has read its S^T / dP^T blocks too: the 16-bit operands may now be
-                // written over them
-                bar_sync(1 + quarter, 64);
-                if (tid == 0) NA2D_TR(3, 4, n);
-
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 3, n);
+                // every S^T / dP^T block of this warp's lanes is in registers: the 16-bit operands
+                // may be written over them
 #pragma unroll
                 for (int a = 0; a < NACT; ++a) {
-                    const int blk = half + 2 * (bi_lo + a);
+                    const int blk = b_lo + a;
                     if (blk < b_hi) {
-                        float l2[16], dl[16];
+                        float l2[8], dl[8];
 #pragma unroll
-                        for (int v4 = 0; v4 < 4; ++v4) {
-                            const float4 x = *reinterpret_cast<const float4*>(s_lse + par * 128 + 16 * blk + 4 * v4);
-                            const float4 y = *reinterpret_cast<const float4*>(s_delta + par * 128 + 16 * blk + 4 * v4);
+                        for (int v4 = 0; v4 < 2; ++v4) {
+                            const float4 x = *reinterpret_cast<const float4*>(x_lse + 8 * blk + 4 * v4);
+                            const float4 y = *reinterpret_cast<const float4*>(x_delta + 8 * blk + 4 * v4);
                             l2[4 * v4] = x.x; l2[4 * v4 + 1] = x.y; l2[4 * v4 + 2] = x.z; l2[4 * v4 + 3] = x.w;
                             dl[4 * v4] = y.x; dl[4 * v4 + 1] = y.y; dl[4 * v4 + 2] = y.z; dl[4 * v4 + 3] = y.w;
                         }
-                        uint32_t wp[8], wd[8], wr2[8];
+                        uint32_t wp[4], wd[4], wr2[4];
 #pragma unroll
-                        for (int e2 = 0; e2 < 8; ++e2) {
+                        for (int e2 = 0; e2 < 4; ++e2) {
                             float p[2], ds[2];
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
@@ -378,57 +487,31 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                             wd[e2] = pack2<DT>(ds[0], ds[1]);
                             wr2[e2] = SPLIT ? pack2_residual_bf16(ds[0], ds[1], wd[e2]) : 0u;
                         }
-                        tmem_st_32x8(tmem_lane + C::TMEM_PT + 8 * blk, wp);
-                        tmem_st_32x8(tmem_lane + C::TMEM_DST + 8 * blk, wd);
-                        if (SPLIT) tmem_st_32x8(tmem_lane + C::TMEM_RES + 8 * blk, wr2);
+                        tmem_st_32x4(tmem_lane + C::TMEM_PT + 4 * blk, wp);
+                        tmem_st_32x4(tmem_lane + C::TMEM_DST + 4 * blk, wd);
+                        if (SPLIT) tmem_st_32x4(tmem_lane + C::TMEM_RES + 4 * blk, wr2);
                     }
                 }
-                {   // own blocks outside the range hold zeros
-                    const uint32_t z[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-                    for (int bi = 0; bi < NBH; ++bi) {
-                        const int blk = half + 2 * bi;
-                        const bool in_range = bi >= bi_lo && bi < bi_lo + NACT && blk < b_hi;
-                        if (!in_range && blk < C::NB16) {
-                            tmem_st_32x8(tmem_lane + C::TMEM_PT + 8 * blk, z);
-                            tmem_st_32x8(tmem_lane + C::TMEM_DST + 8 * blk, z);
-                            if (SPLIT) tmem_st_32x8(tmem_lane + C::TMEM_RES + 8 * blk, z);
+                {   // blocks outside the range hold zeros
+                    const uint32_t z[4] = {0u, 0u, 0u, 0u};
+                    for (int blk = 0; blk < C::NB8; ++blk) {
+                        const bool in_range = blk >= b_lo && blk < b_lo + NACT && blk < b_hi;
+                        if (!in_range) {
+                            tmem_st_32x4(tmem_lane + C::TMEM_PT + 4 * blk, z);
+                            tmem_st_32x4(tmem_lane + C::TMEM_DST + 4 * blk, z);
+                            if (SPLIT) tmem_st_32x4(tmem_lane + C::TMEM_RES + 4 * blk, z);
                         }
                     }
                 }
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_full);
-                if (tid == 0) NA2D_TR(3, 5, n);
+                if (lane == 0) mbar_arrive(p_full + group);
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 5, n);
             }
-
-            // ---- epilogue: this half's columns of the dV and dK rows of the warp's 32 keys
-            mbar_wait(acc_full, it & 1, abort_flag, kErrMmaWait);
-            tc_fence_after();
-            if (tid == 0) NA2D_TR(3, 6, n - 1);
-            {
-                uint8_t* stage = sOut + warp * OutStage<DH>::BYTES;
-                const int h0 = t.kr0 + quarter * (32 / TW);
-                uint32_t acc[DH];
-#pragma unroll
-                for (int which = 0; which < 2; ++which) {
-                    const uint32_t col0 = (which == 0 ? C::TMEM_DV : C::TMEM_DK) + half * DH;
-#pragma unroll
-                    for (int piece = 0; piece < DH / 16; ++piece)
-                        tmem_ld_32x16(tmem_lane + col0 + 16 * piece, *reinterpret_cast<uint32_t(*)[16]>(&acc[16 * piece]));
-                    tmem_ld_wait();
-                    stage_and_store<DT, DH>(which == 0 ? &tm_dv : &tm_dk, stage, acc, 1.f, half * DH, t.kc0, h0, t.bn, lane);
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_free);
-            if (tid == 0) NA2D_TR(3, 7, n - 1);
-            ++it;
         }
     }
 
-    if (warp < 8 && lane == 0) bulk_wait<0>();          // the staging buffers have been read, the rows written
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
@@ -443,8 +526,8 @@ int launch_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, cons
     using C = DkvCfg<D, KS, IsBf16<DT>::value>;
     CUtensorMap tk, tv, tq, tg, tdk, tdv;
     int rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tdk, d_k, dtype, g.BN, g.Hkv, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
-    if (rc == NA2D_OK) rc = make_map(&tdv, d_v, dtype, g.BN, g.Hkv, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
+    if (rc == NA2D_OK) rc = make_map(&tdk, d_k, dtype, g.BN, g.Hkv, g.W, D, TW, 32 / TW, 32);
+    if (rc == NA2D_OK) rc = make_map(&tdv, d_v, dtype, g.BN, g.Hkv, g.W, D, TW, 32 / TW, 32);
     if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, TW, TH);
     if (rc == NA2D_OK) rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, C::HW, C::RC);
     if (rc == NA2D_OK) rc = make_map(&tg, d_o, dtype, g.BN, g.Hq, g.W, D, C::HW, C::RC);
@@ -456,7 +539,8 @@ int launch_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, cons
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return NA2D_ERR_CUDA;
     const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 384, C::SMEM, st>>>(tk, tv, tq, tg, tdk, tdv, lse, delta, (DT*)d_k, (DT*)d_v, g, tiles_r, tiles_c, (int)tiles);
+    kern<<<grid, 512, C::SMEM, st>>>(tk, tv, tq, tg, tdk, tdv, lse, delta, (DT*)d_k, (DT*)d_v, g, tiles_r, tiles_c,
+                                     (int)tiles);
     *launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }
