@@ -194,7 +194,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         // ------------------------------------------------------------------ MMA issue
         // (the whole warp walks the loop so that addresses stay warp-uniform; one lane issues)
         reg_dec<kRegsDonor>();
-        const bool leader = lane == 0;
         constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
         constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
         constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
@@ -207,7 +206,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             tc_fence_after();
             const uint32_t q_lo = smem_desc_lo(smem_u32(sQ + qb * C::Q_BYTES), 16);
             const uint32_t k_lo = smem_desc_lo(smem_u32(sK + sk * C::K_BYTES), 16);
-            if (leader) {
+            if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     constexpr int kPerSlab = C::SLAB_C / 16;
@@ -227,7 +226,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             if (c == 0) mbar_wait(o_free + ob, ((i >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
             tc_fence_after();
             const uint32_t v_lo = smem_desc_lo(smem_u32(sV + sv * C::V_BYTES), C::KV_SLAB);
-            if (leader) {
+            if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < C::NKP / 16; ++kk) {
                     umma_ts(tmem_base + C::TMEM_O0 + ob * C::TMEM_OSTRIDE, tmem_base + C::TMEM_S + 8 * kk,
