@@ -265,6 +265,7 @@ inline bool supported(int dtype, int C, int ks) {
 }  // namespace na2d_tc
 
 #include "na2d_tc_fwd.cuh"
+#include "na2d_tc_dq1.cuh"
 #include "na2d_tc_bwd.cuh"
 #include "na2d_tc_dkdv.cuh"
 

@@ -422,6 +422,11 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 template <typename DT, int D, int KS>
 int launch_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
               const void* d_o, void* d_q, float* delta, int device, cudaStream_t st, int* launched) {
+    // kernel sizes 3 and 5 with a dQ output go to the strip kernel; this one keeps the larger
+    // windows and the delta-only call
+    if constexpr (KS <= 5) {
+        if (d_q != nullptr) return launch_dq1<DT, D, KS>(g, dtype, q, k, v, lse, d_o, d_q, delta, device, st, launched);
+    }
     using C = DqCfg<D, KS, IsBf16<DT>::value>;
     CUtensorMap tq, tg, tk, tv, tdq;
     int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
