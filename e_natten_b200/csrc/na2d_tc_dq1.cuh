@@ -9,7 +9,7 @@
 //     dQ = dS_A K_A + dS_B K_B                  (accumulated over S_B, which is in registers by then)
 // Splitting the box lets the tensor pipe work under the softmax warps: the score MMAs of strip B
 // run while strip A is read, dS_A K_A runs while dS_B is formed, and the score MMAs of the next
-// tile's strip A are issued before this tile's last MMA.  The four strip buffers in shared memory
+// tile run under this tile's epilogue.  The four strip buffers in shared memory
 // change roles from tile to tile (K_A, V_A, K_B, V_B of tile i+1 go where V_A, V_B, K_A, K_B of
 // tile i were), so the next tile's K_A and V_A can be fetched as soon as the score MMAs are done.
 // Twelve warps: 0-7 softmax (warps w and w+4 share 32 queries and split the 16-column blocks),
@@ -182,7 +182,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
-        // Order on the tensor pipe: A1(0) B1(0) | A2(i) A1(i+1) B2(i) B1(i+1) | ...  where x1 are the
+        // Order on the tensor pipe: A1(0) B1(0) | A2(i) B2(i) A1(i+1) B1(i+1) | ...  where x1 are the
         // score MMAs of strip x and x2 its dQ MMAs.  The whole warp walks the loop; one elected lane
         // issues.
         reg_dec<kRegsDonor>();
@@ -206,6 +206,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const uint32_t v_lo = smem_desc_lo(strip_base + sv * C::KV_BYTES, 16);
             const uint32_t t_s = tmem_base + (x ? C::TMEM_SB : C::TMEM_SA), t_dp = tmem_base + (x ? C::TMEM_DPB : C::TMEM_DPA);
             if (elect_one()) {
+                NA2D_TR(2, x ? 2 : 0, i);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     constexpr int kPerSlab = C::SLAB_C / 16;
@@ -218,6 +219,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 umma_commit(s_full + x);
                 umma_commit(st_empty + sv);                          // V_x is only read here
                 if (x == 1) umma_commit(q_empty);                    // last reader of the Q and dO tiles
+                NA2D_TR(2, x ? 3 : 1, i);
             }
             __syncwarp();
         };
@@ -230,6 +232,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const uint32_t km_lo = smem_desc_lo(strip_base + sk * C::KV_BYTES, C::KV_SLAB);
             const uint32_t t_ds = tmem_base + (x ? C::TMEM_DPB : C::TMEM_DPA);
             if (elect_one()) {
+                NA2D_TR(2, x ? 6 : 4, i);
 #pragma unroll
                 for (int kk = 0; kk < C::NKP / 16; ++kk)
                     umma_ts(tmem_base + C::TMEM_DQ, t_ds + 8 * kk, desc64(hi, km_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o,
@@ -242,6 +245,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 }
                 umma_commit(st_empty + sk);
                 if (x == 1) umma_commit(dq_full);
+                NA2D_TR(2, x ? 7 : 5, i);
             }
             __syncwarp();
         };
@@ -251,9 +255,11 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         for (int i = 0; i < n_my; ++i) {
             outputs(i, 0);
-            if (i + 1 < n_my) scores(i + 1, 0);
-            outputs(i, 1);
-            if (i + 1 < n_my) scores(i + 1, 1);
+            outputs(i, 1);                              // dQ complete: the softmax warps wait for it
+            if (i + 1 < n_my) {
+                scores(i + 1, 0);                       // under the epilogue of tile i
+                scores(i + 1, 1);
+            }
         }
     } else if (warp >= 10) {
         reg_dec<kRegsDonor>();
@@ -317,8 +323,10 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                         shl128(m_lo, m_hi, sh);
                     }
                 }
+                if (tid == 0) NA2D_TR(3, x ? 2 : 0, i);
                 mbar_wait(s_full + x, par, abort_flag, kErrMmaWait);
                 tc_fence_after();
+                if (tid == 0) NA2D_TR(3, x ? 3 : 1, i);
 #pragma unroll
                 for (int a = 0; a < NACT; ++a) {
                     const int blk = half + 2 * (bi_lo + a);
@@ -357,6 +365,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             }
             // both strips seen: add the partner's part; both halves now hold delta.  The barrier also
             // tells that the partner has read its blocks, so 16-bit operands may go over them.
+            if (tid == 0) NA2D_TR(3, 4, i);
             x_sum[(par * 2 + half) * 128 + row] = d0 + d1;
             bar_sync(1 + quarter, 64);
             const float dl = (d0 + d1) + x_sum[(par * 2 + (half ^ 1)) * 128 + row];
@@ -398,6 +407,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full + x);
+                if (tid == 0) NA2D_TR(3, x ? 6 : 5, i);
             }
 
             // ---- epilogue: this half's columns of the dQ rows of the warp's 32 queries
@@ -411,6 +421,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dq_free);
+            if (tid == 0) NA2D_TR(3, 7, i);
             stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0, r0 + quarter * (32 / TW), bn,
                                     lane);
         }
