@@ -13,8 +13,8 @@
 // Tensor memory holds two chunk stages (S^T, dP^T of 64 columns each) next to the dV and dK
 // accumulators, so the score MMAs of one chunk run while the softmax warps work on the previous
 // one.  Sixteen warps: 0-3 and 4-7 are two softmax groups that take alternate chunks (a warp owns
-// the 32 keys of its lane quarter), 8 TMA producer (K, V tile; ring of Q / dO chunks), 9 MMA
-// issue, 10-11 idle (register donors), 12-15 epilogue (dV, dK rows -> staging -> TMA store), which
+// the 32 keys of its lane quarter), 8 TMA producer (K, V tile; ring of Q / dO chunks), 9 issues the
+// score MMAs, 10 the output MMAs, 11 idle (register donor), 12-15 epilogue (dV, dK rows -> staging -> TMA store), which
 // overlaps the next tile.  dK and dV accumulate in tensor memory over all chunks of a tile; no
 // atomics.
 #pragma once
@@ -92,7 +92,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     uint64_t* p_full = bars + 6;             // [2]   softmax group -> MMA
     uint64_t* qd_full = bars + 8;            // [4]   TMA -> MMA
     uint64_t* qd_empty = bars + 12;          // [4]   MMA (commit) -> TMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint64_t* st_free = bars + 16;           // [2]   output MMAs (commit) -> score MMAs: the stage is free
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -107,6 +108,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full + i, 1);
             mbar_init(p_full + i, 4);
+            mbar_init(st_free + i, 1);
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(qd_full + i, 1);
@@ -198,27 +200,31 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
             }
         }
     } else if (warp == 9) {
-        // ------------------------------------------------------------------ MMA issue
-        // Per chunk n two batches are issued: the score MMAs of chunk n into stage n & 1 and the
-        // output MMAs of chunk n - 1 out of the other stage.  Neither depends on the other, so
-        // whichever has its inputs first goes first; the score MMAs of chunk n + 1 reuse the stage
-        // of chunk n - 1 and are issued after both.  The whole warp walks this code with uniform
-        // control flow; one elected lane executes the MMA and commit instructions.
+        // ------------------------------------------------------------------ MMA issue: scores
+        // Two warps issue MMAs, so that the bookkeeping of one runs under the MMAs of the other:
+        // this one the score MMAs of chunk n into stage n & 1, as soon as the chunk's Q / dO have
+        // landed and the output MMAs of chunk n - 2 (warp 10) have left the stage.  The whole warp
+        // walks the loop with uniform control flow; one elected lane issues.
         reg_dec<kDkvRegsCtl>();
-        {
-            const uint32_t leader = lane == 0 ? 1u : 0u;
-            constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
-            constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
-            constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
-            const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16), v_lo = smem_desc_lo(smem_u32(sV), 16);
-            const uint32_t qd_base = smem_u32(sQD);
-
-            auto issue_scores = [&](uint32_t n, bool last_of_tile) {
+        constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
+        constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
+        const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16), v_lo = smem_desc_lo(smem_u32(sV), 16);
+        const uint32_t qd_base = smem_u32(sQD);
+        uint32_t n = 0, it = 0;
+        for (int i = 0; i < n_my; ++i) {
+            const TileGeo t = tile_geo(i);
+            if (t.n_ch == 0) continue;
+            for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
                 const uint32_t q_addr = qd_base + (n % NSTQ) * C::STAGE, g_addr = q_addr + C::KV_BYTES;
                 const uint32_t q_lo = smem_desc_lo(q_addr, 16), g_lo = smem_desc_lo(g_addr, 16);
                 const uint32_t tm = tmem_base + (n & 1) * C::TMEM_STAGE;
+                if (lane == 0) NA2D_TR(2, 0, n);
+                if (ch == 0) mbar_wait(kv_full, it & 1, abort_flag, kErrLoadWait);
+                mbar_wait(qd_full + n % NSTQ, (n / NSTQ) & 1, abort_flag, kErrLoadWait);
+                mbar_wait(st_free + (n & 1), ((n >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
                 if (elect_one()) {
+                    // the S^T and dP^T chains alternate
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         constexpr int kPerSlab = C::SLAB_C / 16;
@@ -229,20 +235,37 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                                 desc64(hi, g_lo + ((slab * C::KV_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
                     }
                     umma_commit(s_full + (n & 1));
-                    if (last_of_tile) umma_commit(kv_empty);           // K and V are only read by the score MMAs
+                    if (ch == t.n_ch - 1) umma_commit(kv_empty);       // K and V are only read by the score MMAs
                     NA2D_TR(2, 2, n);
                 }
                 __syncwarp();
-            };
-            auto issue_outputs = [&](uint32_t n, bool first_of_tile, bool last_of_tile) {
+            }
+            ++it;
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------------------------ MMA issue: outputs
+        // dV += P^T dO, dK += dS^T Q of chunk n out of stage n & 1, when the chunk's softmax group
+        // has written the operands (and, for a tile's first chunk, the epilogue has read the
+        // previous tile's accumulators).
+        reg_dec<kDkvRegsCtl>();
+        constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
+        constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
+        const uint32_t qd_base = smem_u32(sQD);
+        uint32_t n = 0, it = 0;
+        for (int i = 0; i < n_my; ++i) {
+            const TileGeo t = tile_geo(i);
+            if (t.n_ch == 0) continue;
+            for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
                 const uint32_t q_addr = qd_base + (n % NSTQ) * C::STAGE, g_addr = q_addr + C::KV_BYTES;
                 const uint32_t qm_lo = smem_desc_lo(q_addr, C::KV_SLAB), gm_lo = smem_desc_lo(g_addr, C::KV_SLAB);
                 const uint32_t tm = tmem_base + (n & 1) * C::TMEM_STAGE;
-                const uint32_t acc = first_of_tile ? 0u : 1u;
+                const uint32_t acc = ch == 0 ? 0u : 1u;
+                mbar_wait(p_full + (n & 1), (n >> 1) & 1, abort_flag, kErrMmaWait);
+                if (ch == 0) mbar_wait(acc_free, (it & 1) ^ 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
                 if (elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < C::NKP / 16; ++kk) {
+                    for (int kk = 0; kk < C::NKP / 16; ++kk) {               // dK and dV chains alternate
                         umma_ts(tmem_base + C::TMEM_DK, tm + C::TMEM_DST + 8 * kk,
                                 desc64(hi, qm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
                         umma_ts(tmem_base + C::TMEM_DV, tm + C::TMEM_PT + 8 * kk,
@@ -255,69 +278,15 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                                     desc64(hi, qm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, 1u);
                     }
                     umma_commit(qd_empty + (n % NSTQ));
-                    if (last_of_tile) umma_commit(acc_full);
+                    umma_commit(st_free + (n & 1));
+                    if (ch == t.n_ch - 1) umma_commit(acc_full);
                     NA2D_TR(2, 4, n);
                 }
                 __syncwarp();
-            };
-
-            uint32_t n = 0, it = 0;
-            bool have_prev = false, prev_first = false, prev_last = false;
-            uint32_t prev_it = 0;
-            bool gave_up = false;
-            // Issues the score MMAs of chunk n (when `scores`) and the output MMAs of chunk n - 1
-            // (when there is one), in the order their inputs arrive.  Every lane tests the
-            // barriers; a batch goes out when all lanes have seen its inputs.
-            auto step = [&](bool scores, bool first, bool last) {
-                bool done_x = !scores, done_y = !have_prev;
-                const uint32_t limit = (*abort_flag != 0 || gave_up) ? kSpinLimitAborted : kSpinLimit;
-                uint32_t spins = 0;
-                if (leader) NA2D_TR(2, 0, n);
-                while (!(done_x && done_y)) {
-                    if (!done_x) {
-                        const bool ready = mbar_test(qd_full + n % NSTQ, (n / NSTQ) & 1) && (!first || mbar_test(kv_full, it & 1));
-                        if (__all_sync(0xffffffffu, ready)) {
-                            issue_scores(n, last);
-                            done_x = true;
-                        }
-                    }
-                    if (!done_y) {
-                        const bool ready = mbar_test(p_full + ((n - 1) & 1), ((n - 1) >> 1) & 1) &&
-                                           (!prev_first || mbar_test(acc_free, (prev_it & 1) ^ 1));
-                        if (__all_sync(0xffffffffu, ready)) {
-                            issue_outputs(n - 1, prev_first, prev_last);
-                            done_y = true;
-                        }
-                    }
-                    if (++spins > limit) {                              // give up: later waits are short
-                        if (leader) {
-                            *abort_flag = 1;
-                            atomicOr(&g_error_word, kErrMmaWait);
-                        }
-                        gave_up = true;
-                        break;
-                    }
-                    if (spins > 4096) __nanosleep(32);
-                }
-            };
-            for (int i = 0; i < n_my; ++i) {
-                const TileGeo t = tile_geo(i);
-                if (t.n_ch == 0) continue;
-                for (int ch = 0; ch < t.n_ch; ++ch) {
-                    const bool first = ch == 0, last = ch == t.n_ch - 1;
-                    step(true, first, last);
-                    have_prev = true;
-                    prev_first = first;
-                    prev_last = last;
-                    prev_it = it;
-                    ++n;
-                }
-                ++it;
             }
-            step(false, false, false);                                  // output MMAs of the last chunk
+            ++it;
         }
-        __syncwarp();
-    } else if (warp == 10 || warp == 11) {
+    } else if (warp == 11) {
         reg_dec<kDkvRegsCtl>();
     } else if (warp >= 12) {
         // ------------------------------------------------------------------ epilogue warps
