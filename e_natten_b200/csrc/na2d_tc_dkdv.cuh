@@ -13,8 +13,8 @@
 // Tensor memory holds two chunk stages (S^T, dP^T of 64 columns each) next to the dV and dK
 // accumulators, so the score MMAs of one chunk run while the softmax warps work on the previous
 // one.  Sixteen warps: 0-3 and 4-7 are two softmax groups that take alternate chunks (a warp owns
-// the 32 keys of its lane quarter), 8 TMA producer (K, V tile; ring of Q / dO chunks), 9 issues the
-// score MMAs, 10 the output MMAs, 11 idle (register donor), 12-15 epilogue (dV, dK rows -> staging -> TMA store), which
+// the 32 keys of its lane quarter), 8 TMA producer of the Q / dO chunk ring, 11 TMA producer of the
+// K, V tile, 9 issues the score MMAs, 10 the output MMAs, 12-15 epilogue (dV, dK rows -> staging -> TMA store), which
 // overlaps the next tile.  dK and dV accumulate in tensor memory over all chunks of a tile; no
 // atomics.
 #pragma once
@@ -168,25 +168,19 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     };
 
     if (warp == 8) {
-        // ------------------------------------------------------------------ producer
+        // ------------------------------------------------------------------ producer of the Q / dO chunk ring
+        // (the K, V tile has a producer of its own, warp 11: a chunk of the next tile can be
+        // fetched as soon as a ring slot is free, long before the K, V buffers are)
         reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
-            uint32_t n = 0, it = 0;                     // chunk counter, non-empty tile counter
+            uint32_t n = 0;
             for (int i = 0; i < n_my; ++i) {
                 const TileGeo t = tile_geo(i);
-                if (t.n_ch == 0) continue;
-                mbar_wait(kv_empty, (it & 1) ^ 1, abort_flag, kErrLoadWait);
-                mbar_expect_tx(kv_full, 2u * C::Q_BYTES);
-#pragma unroll
-                for (int s = 0; s < C::NS; ++s) {
-                    tma_load_4d(sK + s * C::Q_SLAB, &tm_k, kv_full, s * 64, t.kc0, t.kr0, t.bn);
-                    tma_load_4d(sV + s * C::Q_SLAB, &tm_v, kv_full, s * 64, t.kc0, t.kr0, t.bn);
-                }
-                ++it;
                 for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
                     const int rc = ch / t.n_cc, cc = ch - rc * t.n_cc;
                     const uint32_t st = n % NSTQ;
                     mbar_wait(qd_empty + st, ((n / NSTQ) & 1) ^ 1, abort_flag, kErrLoadWait);
+                    NA2D_TR(2, 7, n);
                     mbar_expect_tx(qd_full + st, 2u * C::NS * C::NK * C::ROWB);
                     uint8_t* dst = sQD + st * C::STAGE;
 #pragma unroll
@@ -220,8 +214,11 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 const uint32_t tm = tmem_base + (n & 1) * C::TMEM_STAGE;
                 if (lane == 0) NA2D_TR(2, 0, n);
                 if (ch == 0) mbar_wait(kv_full, it & 1, abort_flag, kErrLoadWait);
+                if (lane == 0) NA2D_TR(2, 1, n);
                 mbar_wait(qd_full + n % NSTQ, (n / NSTQ) & 1, abort_flag, kErrLoadWait);
+                if (lane == 0) NA2D_TR(2, 3, n);
                 mbar_wait(st_free + (n & 1), ((n >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
+                if (lane == 0) NA2D_TR(2, 5, n);
                 tc_fence_after();
                 if (elect_one()) {
                     // the S^T and dP^T chains alternate
@@ -287,7 +284,23 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
             ++it;
         }
     } else if (warp == 11) {
+        // ------------------------------------------------------------------ producer of the K, V tile
         reg_dec<kDkvRegsCtl>();
+        if (lane == 0) {
+            uint32_t it = 0;                            // non-empty tile counter
+            for (int i = 0; i < n_my; ++i) {
+                const TileGeo t = tile_geo(i);
+                if (t.n_ch == 0) continue;
+                mbar_wait(kv_empty, (it & 1) ^ 1, abort_flag, kErrLoadWait);
+                mbar_expect_tx(kv_full, 2u * C::Q_BYTES);
+#pragma unroll
+                for (int s = 0; s < C::NS; ++s) {
+                    tma_load_4d(sK + s * C::Q_SLAB, &tm_k, kv_full, s * 64, t.kc0, t.kr0, t.bn);
+                    tma_load_4d(sV + s * C::Q_SLAB, &tm_v, kv_full, s * 64, t.kc0, t.kr0, t.bn);
+                }
+                ++it;
+            }
+        }
     } else if (warp >= 12) {
         // ------------------------------------------------------------------ epilogue warps
         reg_dec<kDkvRegsEpi>();
