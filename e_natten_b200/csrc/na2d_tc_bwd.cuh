@@ -187,7 +187,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                     }
                 }
                 tc_fence_after();
-                if (leader) {
+                if (elect_one()) {
                     NA2D_TR(2, 1, n);
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
@@ -215,7 +215,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 ++n_p;
                 if (!C::ONE && u == NCH && i > 0) mbar_wait(dq_free, (i & 1) ^ 1, abort_flag, kErrMmaWait);
                 tc_fence_after();
-                if (leader) {
+                if (elect_one()) {
                     NA2D_TR(2, 3, n);
                     const uint32_t acc = (!C::ONE && u > NCH) ? 1u : 0u;
 #pragma unroll
