@@ -302,6 +302,26 @@ def test_autograd_semantics_match_the_reference_entry_point():
     assert_close(lse, rlse, torch.float32, "lse")
 
 
+@pytest.mark.parametrize("ks", [5, 9])
+def test_delta_only_call_matches_the_full_call(ks):
+    """`na2d_backward_dq` without a dQ buffer only writes the row deltas (sum_j p_j dP_j, equal to
+    dO . o); with a buffer it writes both.  The two calls may run different kernels."""
+    dtype = torch.bfloat16
+    q, k, v, d_o = make_inputs((1, 2, 40, 24, 64), dtype, 17, q_scale=0.125)
+    qd, kd, vd, gd = (t.to(DEV) for t in (q, k, v, d_o))
+    o, lse = na.natten2d_forward(qd, kd, vd, ks)
+    delta_only = torch.full_like(lse, float("nan"))
+    na.functional.backward_dq_into(qd, kd, vd, o, lse, gd, None, delta_only, ks)
+    dq = torch.empty_like(qd)
+    delta_full = torch.full_like(lse, float("nan"))
+    na.functional.backward_dq_into(qd, kd, vd, o, lse, gd, dq, delta_full, ks)
+    na.check_kernels(DEV)
+    ro, _, _, _, _ = orc.natten2d_fwd_bwd(q, k, v, d_o, ks)
+    want = (d_o.double() * ro).sum(-1)
+    assert_close(delta_only, want, dtype, "delta (delta-only call)")
+    assert_close(delta_full, want, dtype, "delta (full call)")
+
+
 def test_entry_points_work_from_a_thread_that_made_no_cuda_call():
     """An autograd worker thread may reach the library before any runtime call has bound the
     device's context to it; the tensor-core launchers (which encode tensor maps through the

@@ -98,14 +98,17 @@ def test_row_sharded_bands_equal_whole_image(world, H, W, ks):
 def _lonely_worker(rank, world, port, result):
     """Rank 1 leaves before the exchange; rank 0 must get an error from its bounded wait, not hang."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    # generous rendezvous (a loaded host can start the two processes seconds apart), short waits for
+    # the exchange itself
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+    group = dist.new_group(timeout=datetime.timedelta(seconds=5))
     if rank == 1:
         os._exit(0)                                   # a rank that never takes part in the exchange
     q, k, v, _ = orc.round_inputs((1, 1, 20, 8, 2), torch.float64, 3)
     sh = sharding.plan_row_shard(20, world, rank, 5)
     band = slice(sh.row0, sh.row0 + sh.R)
     try:
-        sharding.exchange_kv_halo(k[:, :, band].contiguous(), v[:, :, band].contiguous(), sh)
+        sharding.exchange_kv_halo(k[:, :, band].contiguous(), v[:, :, band].contiguous(), sh, group)
         result.put("no error")
     except Exception as exc:                          # noqa: BLE001 - any error from the transport is the point
         result.put("error: " + type(exc).__name__)
@@ -120,6 +123,6 @@ def test_missing_neighbour_is_an_error_not_a_hang():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout=90)
+        p.join(timeout=200)
     assert all(not p.is_alive() for p in procs)
     assert result.get(timeout=5).startswith("error")
