@@ -262,10 +262,26 @@ inline bool supported(int dtype, int C, int ks) {
         default: return NA2D_ERR_UNSUPPORTED;                                 \
     }
 
+
+#ifdef NA2D_TRACE
+// Development aid (not compiled into the shipped library): CTA 0 records the SM clock at the
+// hand-overs between the warps so that they can be laid out on a time line.
+__device__ unsigned long long g_trace[8192];     // [role 0..3][unit 0..255][event 0..7]
+__device__ unsigned int g_trace_n = 8192;
+__device__ __forceinline__ void trace(int role, int ev, unsigned n) {
+    if (blockIdx.x != 0 || n >= 256) return;
+    g_trace[(role * 256 + n) * 8 + ev] = clock64();
+}
+#define NA2D_TR(role, ev, n) trace(role, ev, n)
+#else
+#define NA2D_TR(role, ev, n)
+#endif
+
 }  // namespace na2d_tc
 
-#include "na2d_tc_fwd.cuh"
 #include "na2d_tc_dq1.cuh"
+#include "na2d_tc_fwd1.cuh"
+#include "na2d_tc_fwd.cuh"
 #include "na2d_tc_bwd.cuh"
 #include "na2d_tc_dkdv.cuh"
 

@@ -25,19 +25,6 @@
 
 namespace na2d_tc {
 
-#ifdef NA2D_TRACE
-// Development aid (not compiled into the shipped library): CTA 0 records the SM clock at the
-// hand-overs between the warps so that they can be laid out on a time line.
-__device__ unsigned long long g_trace[8192];     // [role 0..3][unit 0..255][event 0..7]
-__device__ unsigned int g_trace_n = 8192;
-__device__ __forceinline__ void trace(int role, int ev, unsigned n) {
-    if (blockIdx.x != 0 || n >= 256) return;
-    g_trace[(role * 256 + n) * 8 + ev] = clock64();
-}
-#define NA2D_TR(role, ev, n) trace(role, ev, n)
-#else
-#define NA2D_TR(role, ev, n)
-#endif
 
 template <int D, int KS>
 struct FwdCfg : Cfg<D, KS, 256> {
@@ -458,6 +445,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 template <typename DT, int D, int KS>
 int launch_forward(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
                    int device, cudaStream_t st, int* launched) {
+    // kernel sizes 3 and 5 go to the strip kernel
+    if constexpr (KS <= 5) return launch_forward1<DT, D, KS>(g, dtype, q, k, v, o, lse, device, st, launched);
     using C = FwdCfg<D, KS>;
     CUtensorMap tq, tk, tv, to;
     int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
