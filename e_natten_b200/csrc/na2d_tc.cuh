@@ -222,6 +222,12 @@ inline int make_map(CUtensorMap* map, const void* base, int dtype, long long BN,
 constexpr int kRegsLaunch = 168, kRegsDonor = 64, kRegsSoftmax = 216;
 static_assert((kRegsSoftmax - kRegsLaunch) * 8 <= (kRegsLaunch - kRegsDonor) * 4, "setmaxnreg.inc would wait for ever");
 
+// The same for the kernels of sixteen warps (512 threads, launched with 128 registers each): softmax
+// warps, control warps (producers, MMA issue) and epilogue warps.
+constexpr int kDkvRegsLaunch = 128, kDkvRegsSoftmax = 176, kDkvRegsCtl = 72, kDkvRegsEpi = 88;
+static_assert((kDkvRegsSoftmax - kDkvRegsLaunch) * 8 <= (kDkvRegsLaunch - kDkvRegsCtl) * 4 + (kDkvRegsLaunch - kDkvRegsEpi) * 4,
+              "setmaxnreg.inc would wait for ever");
+
 constexpr int kSmemLimit = 232448;     // dynamic shared memory a CTA can opt in to on sm_100
 
 // Number of SMs of `device` (persistent kernels launch one CTA per SM), cached.

@@ -41,11 +41,6 @@ constexpr unsigned long long row_repeat(int hw, int rc) {
     return m;
 }
 
-// Registers per thread after re-balancing (512 threads are launched with 128 each).
-constexpr int kDkvRegsLaunch = 128, kDkvRegsSoftmax = 176, kDkvRegsCtl = 72, kDkvRegsEpi = 88;
-static_assert((kDkvRegsSoftmax - kDkvRegsLaunch) * 8 <= (kDkvRegsLaunch - kDkvRegsCtl) * 4 + (kDkvRegsLaunch - kDkvRegsEpi) * 4,
-              "setmaxnreg.inc would wait for ever");
-
 template <int D, int KS, bool SPLIT>
 struct DkvCfg : Cfg<D, KS, 64, 0, dkv_w_split(KS)> {
     using B = Cfg<D, KS, 64, 0, dkv_w_split(KS)>;

@@ -9,10 +9,11 @@
 // Tensor memory holds three strip buffers and O.  A tile uses two of the strip buffers, the next
 // tile's S_A goes into the third one and its S_B into the buffer P_A V_A has just left, so the
 // score MMAs of tile i+1 run while the softmax warps work on tile i, and P V of tile i runs while
-// they read tile i+1.  The output of tile i is normalised and stored after P of tile i+1 has
-// been handed over (its P V must wait for O to be read, nothing else does).
-// Twelve warps: 0-7 softmax (warps w and w+4 share 32 queries and split the 16-column blocks),
-// 8 TMA producer (Q, K strips), 10 TMA producer (V strips), 9 MMA issue, 11 idle (register donor).
+// they read tile i+1.  Four epilogue warps normalise and store the output of tile i meanwhile
+// (the next tile's P V waits for O to be read, nothing else does).
+// Sixteen warps: 0-7 softmax (warps w and w+4 share 32 queries and split the 16-column blocks),
+// 8 TMA producer (Q, K strips), 10 TMA producer (V strips), 9 MMA issue, 11 idle (register donor),
+// 12-15 epilogue (one per tensor-memory lane quarter).
 #pragma once
 
 namespace na2d_tc {
@@ -23,8 +24,8 @@ struct Fwd1Cfg : Cfg<D, KS, 128, 0, 2> {
     static_assert(B::NCH == 1, "a strip must hold all box rows");
     static constexpr int TMEM_STRIP = 128;                               // three strip buffers at 0, 128, 256
     static constexpr int TMEM_O = 384;
-    static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;         // output staging of the 8 softmax warps
-    static constexpr int XCHG_BYTES = 4 * 2 * 128 * 4;                   // row max [2][2][128], row sum [2][2][128]
+    static constexpr int OUT_BYTES = 4 * OutStage<32>::BYTES;            // output staging of the 4 epilogue warps
+    static constexpr int XCHG_BYTES = (4 * 2 + 2) * 128 * 4;             // row max [2][2][128], row sum [2][2][128], final max [2][128]
     static constexpr int SMEM = B::Q_BYTES + 4 * B::KV_BYTES + OUT_BYTES + XCHG_BYTES + 256 + 1024;
     static constexpr int NB16 = B::NKP / 16;
     static constexpr unsigned long long REP_LO = row_repeat_lo(B::HW, KS), REP_HI = row_repeat_hi(B::HW, KS);
@@ -33,7 +34,7 @@ struct Fwd1Cfg : Cfg<D, KS, 128, 0, 2> {
 };
 
 template <typename DT, int D, int KS>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(512, 1)
 fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
             const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
             float* __restrict__ lse, const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
@@ -45,7 +46,8 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     uint8_t* sOut = sKV + 4 * C::KV_BYTES;                // 8 x output staging (1024-byte aligned)
     float* x_max = reinterpret_cast<float*>(sOut + C::OUT_BYTES);     // [tile parity][half][row]
     float* x_sum = x_max + 2 * 2 * 128;                               // [tile parity][half][row]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(x_sum + 2 * 2 * 128);
+    float* x_fin = x_sum + 2 * 2 * 128;                               // [tile parity][row]  final max * log2(e)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_fin + 2 * 128);
     uint64_t* q_full = bars + 0;             //      TMA -> MMA
     uint64_t* q_empty = bars + 1;            //      MMA (commit) -> TMA
     uint64_t* o_full = bars + 2;             //      MMA (commit) -> softmax
@@ -65,7 +67,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         mbar_init(q_full, 1);
         mbar_init(q_empty, 1);
         mbar_init(o_full, 1);
-        mbar_init(o_free, 8);
+        mbar_init(o_free, 4);
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full + i, 1);
             mbar_init(p_full + i, 8);
@@ -88,7 +90,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     // Rows [NK, NKP) of the V strips are contraction rows of O = P V that TMA never writes: zero them once.
     if constexpr (C::NKP > C::NK) {
         constexpr int pad16 = (C::NKP - C::NK) * C::ROWB / 16;
-        for (int i = tid; i < 2 * C::NS * pad16; i += 384) {
+        for (int i = tid; i < 2 * C::NS * pad16; i += 512) {
             const int which = i / pad16, off = i - which * pad16;           // which = strip * NS + slab
             st_shared_v4(smem_u32(sKV + (2 + which / C::NS) * C::KV_BYTES + (which % C::NS) * C::KV_SLAB +
                                   C::NK * C::ROWB + off * 16), 0u, 0u, 0u, 0u);
@@ -116,7 +118,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         // Warp 8 fetches the Q tile and the K strips, whose buffers the score MMAs release early in
         // a tile; warp 10 the V strips, whose buffers are only released by P V.  One producer for
         // both would hold the next tile's Q and K back behind the wait for a V buffer.
-        reg_dec<kRegsDonor>();
+        reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
             const int j0 = warp == 8 ? 0 : 2;
             for (int i = 0; i < n_my; ++i) {
@@ -151,7 +153,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         // ------------------------------------------------------------------ MMA issue
         // Order on the tensor pipe: S_A(0) S_B(0) | S_A(i+1) PV_A(i) S_B(i+1) PV_B(i) | ...
         // The whole warp walks the loop; one elected lane issues.
-        reg_dec<kRegsDonor>();
+        reg_dec<kDkvRegsCtl>();
         constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
         constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
         constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
@@ -212,45 +214,54 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             outputs(i, 1);
         }
     } else if (warp == 11) {
-        reg_dec<kRegsDonor>();
+        reg_dec<kDkvRegsCtl>();
+    } else if (warp >= 12) {
+        // ------------------------------------------------------------------ epilogue warps
+        reg_dec<kDkvRegsEpi>();
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                 // query of the tile = tensor-memory lane
+        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        uint8_t* stage = sOut + quarter * OutStage<32>::BYTES;
+        constexpr int RPO = D / 32;                          // 32-channel rounds
+        for (int i = 0; i < n_my; ++i) {
+            int bn, r0, c0;
+            decode(i, bn, r0, c0);
+            const uint32_t par = i & 1;
+            const int qr = r0 + (row / TW), qc = c0 + (row % TW);
+            mbar_wait(o_full, par, abort_flag, kErrMmaWait);            // also: the softmax warps' sums are written
+            tc_fence_after();
+            const float total = x_sum[(par * 2 + 0) * 128 + row] + x_sum[(par * 2 + 1) * 128 + row];
+            const float fin = x_fin[par * 128 + row];
+            const float inv = 1.f / total;
+            uint32_t v[2][32];
+            tmem_ld_32x32(tmem_lane + C::TMEM_O, v[0]);
+#pragma unroll
+            for (int j = 0; j < RPO; ++j) {
+                tmem_ld_wait();
+                if (j + 1 < RPO) {
+                    tmem_ld_32x32(tmem_lane + C::TMEM_O + 32 * (j + 1), v[(j + 1) & 1]);
+                } else {                                     // O is in registers
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(o_free);
+                }
+                stage_and_store<DT, 32>(&tm_o, stage, v[j & 1], inv, 32 * j, c0, r0 + quarter * (32 / TW), bn, lane);
+            }
+            if (qr < g.Hq && qc < g.W)
+                lse[(static_cast<size_t>(bn) * g.Hq + qr) * g.W + qc] = (fin + log2f(total)) * kLn2;
+        }
+        if (lane == 0) bulk_wait<0>();                       // the staging buffer has been read, the rows written
     } else {
         // ------------------------------------------------------------------ softmax warps
-        reg_inc<kRegsSoftmax>();
+        reg_inc<kDkvRegsSoftmax>();
         const int quarter = warp & 3, half = warp >> 2;
         const int row = quarter * 32 + lane;                 // query of the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        constexpr int DH = D / 2;                            // output columns of this half
         constexpr int NBH = (C::NB16 + 1) / 2;               // own blocks of a strip at most
         constexpr int kRows = (32 / TW - 1 + KS) < C::RC ? (32 / TW - 1 + KS) : C::RC;
         constexpr int kBlocks = (kRows * C::HW - 1) / 16 + 2;
         constexpr int NACT = (kBlocks + 1) / 2 < NBH ? (kBlocks + 1) / 2 : NBH;
         constexpr unsigned long long kRepLo = C::REP_LO, kRepHi = C::REP_HI;   // bit r * HW for the ks window rows
-
-        // the previous tile's output, stored one tile late (see the head of the file)
-        bool pend = false, pend_valid = false;
-        uint32_t pend_par = 0;
-        float pend_max = 0.f, pend_sum = 1.f;
-        size_t pend_qi = 0;
-        int pend_bn = 0, pend_r0 = 0, pend_c0 = 0;
-        auto epilogue = [&]() {
-            bar_sync(1 + quarter, 64);                                       // partner's row sum is in x_sum
-            const float total = pend_sum + x_sum[(pend_par * 2 + (half ^ 1)) * 128 + row];
-            mbar_wait(o_full, pend_par, abort_flag, kErrMmaWait);
-            tc_fence_after();
-            const float inv = 1.f / total;
-            uint32_t acc[DH];
-#pragma unroll
-            for (int piece = 0; piece < DH / 16; ++piece)
-                tmem_ld_32x16(tmem_lane + C::TMEM_O + half * DH + 16 * piece, *reinterpret_cast<uint32_t(*)[16]>(&acc[16 * piece]));
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_free);                              // O is in registers
-            stage_and_store<DT, DH>(&tm_o, sOut + warp * OutStage<DH>::BYTES, acc, inv, half * DH, pend_c0,
-                                    pend_r0 + quarter * (32 / TW), pend_bn, lane);
-            if (pend_valid && half == 0) lse[pend_qi] = (pend_max + log2f(total)) * kLn2;
-            pend = false;
-        };
 
         for (int i = 0; i < n_my; ++i) {
             int bn, r0, c0;
@@ -259,7 +270,6 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
             const int qr_raw = r0 + (row / TW), qc_raw = c0 + (row % TW);
-            const bool q_valid = qr_raw < g.Hq && qc_raw < g.W;
             const int qr = min(qr_raw, g.Hq - 1), qc = min(qc_raw, g.W - 1);
             const int wr = na2d_ws(g.q_row0 + qr, g.Hg, KS) - g.kv_row0 - box_r0;   // in [0, TH)
             const int wc = na2d_ws(qc, g.W, KS) - box_c0;                            // in [0, TW)
@@ -368,29 +378,19 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                         if (!in_range && 16 * blk < C::NKP) tmem_st_32x8(t_s + 8 * blk, z);
                     }
                 }
+                if (x == 1) {
+                    // what the epilogue warps need, written before the arrival that lets the last
+                    // P V go: this half's row sum, and the row maximum
+                    x_sum[(par * 2 + half) * 128 + row] = c0s + c1s;
+                    if (half == 0) x_fin[par * 128 + row] = safe_max;
+                }
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full + x);
                 if (tid == 0) NA2D_TR(3, x ? 6 : 5, i);
             }
-            const float run_sum = c0s + c1s;
-            x_sum[(par * 2 + half) * 128 + row] = run_sum;
-
-            if (pend) epilogue();               // the previous tile's output; frees O for this tile's P V
-            if (tid == 0) NA2D_TR(3, 7, i);
-            pend = true;
-            pend_par = par;
-            pend_bn = bn;
-            pend_r0 = r0;
-            pend_c0 = c0;
-            pend_valid = q_valid;
-            pend_max = safe_max;
-            pend_sum = run_sum;
-            pend_qi = (static_cast<size_t>(bn) * g.Hq + qr) * g.W + qc;
         }
-        if (pend) epilogue();
-        if (lane == 0) bulk_wait<0>();          // the staging buffer has been read, the rows written
     }
 
     tc_fence_before();
@@ -407,7 +407,7 @@ int launch_forward1(const Na2dGeom& g, int dtype, const void* q, const void* k, 
     using C = Fwd1Cfg<D, KS>;
     CUtensorMap tq, tk, tv, to;
     int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&to, o, dtype, g.BN, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
+    if (rc == NA2D_OK) rc = make_map(&to, o, dtype, g.BN, g.Hq, g.W, D, TW, 32 / TW, 32);
     if (rc == NA2D_OK) rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc != NA2D_OK) return rc;
@@ -418,7 +418,7 @@ int launch_forward1(const Na2dGeom& g, int dtype, const void* q, const void* k, 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return NA2D_ERR_CUDA;
     const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 384, C::SMEM, st>>>(tq, tk, tv, to, lse, g, tiles_r, tiles_c, (int)tiles);
+    kern<<<grid, 512, C::SMEM, st>>>(tq, tk, tv, to, lse, g, tiles_r, tiles_c, (int)tiles);
     *launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }
