@@ -68,7 +68,7 @@ def algorithmic_bytes(B, N, H, W, C, esize):
 # DRAM bytes (read + written) per launch, per byte of one (B, N, H, W, C) tensor, from one ncu
 # capture of workload c2 at side 128 (profiles/tcgen05_fwd_dq_dkdv_c2_bf16.md).  Reads equal the
 # input bytes, so the traffic of the other c2 sides follows in proportion to the tensor size.
-NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"na2d forward": 3.637, "na2d backward dQ": 4.759, "na2d backward dK/dV": 5.578}
+NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"na2d forward": 3.652, "na2d backward dQ": 4.786, "na2d backward dK/dV": 5.554}
 NCU_TRAFFIC_SOURCE = "ncu capture of c2-128 scaled by tensor bytes"
 
 
