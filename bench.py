@@ -50,6 +50,7 @@ WORKLOADS = {
     "c4a": (16, 8, 28, 28, 64, 13, "bf16", 2, 1.0, 1.0),
     "c4b": (16, 16, 14, 14, 64, 13, "bf16", 2, 1.0, 1.0),
     "c5": (1, 8, 1024, 1024, 128, 13, "bf16", 3, 1.0, 1.0),
+    "c5-256": (1, 8, 256, 256, 128, 13, "bf16", 3, 1.0, 1.0),           # c5 at a size an ncu capture can hold
 }
 FALLBACK_HBM_GBS = 6650.0
 
