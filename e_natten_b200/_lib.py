@@ -24,6 +24,28 @@ class Rows(C.Structure):
                 ("H_global", C.c_int)]
 
 
+class TensorDesc(C.Structure):
+    """Mirror of ``na2d_tensor``: device pointer and element strides (batch, head, row, column);
+    all strides zero means dense."""
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_n", C.c_int64),
+                ("stride_h", C.c_int64), ("stride_w", C.c_int64)]
+
+
+class Args(C.Structure):
+    """Mirror of ``na2d_args``: everything one of the ``*_ex`` entry points needs."""
+    _fields_ = [("struct_size", C.c_size_t), ("op", C.c_int),
+                ("B", C.c_int), ("N", C.c_int), ("H", C.c_int), ("W", C.c_int), ("C", C.c_int),
+                ("kernel_size", C.c_int), ("dtype", C.c_int), ("path", C.c_int), ("device", C.c_int),
+                ("scale", C.c_float), ("stream", C.c_void_p), ("rows", C.POINTER(Rows)),
+                ("q", TensorDesc), ("k", TensorDesc), ("v", TensorDesc), ("o", TensorDesc),
+                ("d_o", TensorDesc), ("d_q", TensorDesc), ("d_k", TensorDesc), ("d_v", TensorDesc),
+                ("lse", C.c_void_p), ("delta", C.c_void_p)]
+
+
+OP_2D, OP_1D = 0, 1
+_DENSE = [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]      # B..dtype, rows, path, device, stream
+_PAIR = [C.c_int] * 7 + [C.c_int, C.c_void_p]                                  # B..dtype, device, stream
+
 # name -> (restype, argtypes); every symbol include/na2d.h declares
 SIGNATURES = {
     "na2d_version": (C.c_int, []),
@@ -32,12 +54,24 @@ SIGNATURES = {
     "na2d_window_start": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "na2d_backward_window": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "na2d_dump_index": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
-    "na2d_forward": (C.c_int, [C.c_void_p] * 5 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
-    "na2d_backward_dq": (C.c_int, [C.c_void_p] * 8 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
-    "na2d_backward_dkdv": (C.c_int, [C.c_void_p] * 8 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
-    "na2d_backward": (C.c_int, [C.c_void_p] * 10 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
-    "na2d_backward_static_scratch": (C.c_int, [C.c_void_p] * 9 + [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]),
+    "na2d_forward": (C.c_int, [C.c_void_p] * 5 + _DENSE),
+    "na2d_backward_dq": (C.c_int, [C.c_void_p] * 8 + _DENSE),
+    "na2d_backward_dkdv": (C.c_int, [C.c_void_p] * 8 + _DENSE),
+    "na2d_backward": (C.c_int, [C.c_void_p] * 10 + _DENSE),
+    "na2d_backward_static_scratch": (C.c_int, [C.c_void_p] * 9 + _DENSE),
+    "na2d_forward_ex": (C.c_int, [C.POINTER(Args)]),
+    "na2d_backward_dq_ex": (C.c_int, [C.POINTER(Args)]),
+    "na2d_backward_dkdv_ex": (C.c_int, [C.POINTER(Args)]),
+    "na2d_backward_ex": (C.c_int, [C.POINTER(Args)]),
+    "na1d_forward": (C.c_int, [C.c_void_p] * 5 + [C.c_int] * 6 + [C.c_int, C.c_void_p]),
+    "na1d_backward": (C.c_int, [C.c_void_p] * 10 + [C.c_int] * 6 + [C.c_int, C.c_void_p]),
+    "na2d_qk_forward": (C.c_int, [C.c_void_p] * 3 + _PAIR),
+    "na2d_qk_backward": (C.c_int, [C.c_void_p] * 5 + _PAIR),
+    "na2d_av_forward": (C.c_int, [C.c_void_p] * 3 + _PAIR),
+    "na2d_av_backward": (C.c_int, [C.c_void_p] * 5 + _PAIR),
     "na2d_check": (C.c_int, [C.c_int, C.c_void_p]),
+    "na2d_poll": (C.c_int, [C.c_int, C.c_void_p]),
+    "na2d_selftest_wait_timeout": (C.c_int, [C.c_int, C.c_void_p, C.c_uint]),
     "na2d_launch_count": (C.c_longlong, []),
 }
 

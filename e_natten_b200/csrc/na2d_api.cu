@@ -6,11 +6,13 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "../../include/na2d.h"
+#include "na2d_delta.cuh"
 #include "na2d_index.cuh"
 #include "na2d_simt.cuh"
-#include "na2d_tc.cuh"
+#include "na2d_tc_entry.h"
 
 namespace {
 
@@ -57,11 +59,13 @@ struct DeviceScope {
     }
 };
 
+constexpr int kMaxDevices = 64;
+
 // Compute-capability check, cached per device.
 int check_device(int device) {
     static std::mutex mu;
-    static int state[64];   // 0 unknown, 1 ok, 2 not sm_100
-    if (device < 0 || device >= 64) return NA2D_ERR_BAD_ARG;
+    static int state[kMaxDevices];   // 0 unknown, 1 ok, 2 not sm_100
+    if (device < 0 || device >= kMaxDevices) return NA2D_ERR_BAD_ARG;
     std::lock_guard<std::mutex> lock(mu);
     if (state[device] == 0) {
         int major = 0;
@@ -72,37 +76,136 @@ int check_device(int device) {
     return state[device] == 1 ? NA2D_OK : NA2D_ERR_NO_DEVICE;
 }
 
-struct Problem {
-    Na2dGeom g;
-    int dtype;
-    bool tensor;      // run the tcgen05 kernels
+// ---- device error word ---------------------------------------------------------------------------
+// One word per device (a file-scope device variable has one instance per device context); bits
+// say which kind of bounded wait gave up.  Kernels get its address as an argument.
+__device__ unsigned int g_error_word = 0;
+
+// Device address of g_error_word on `device` (which must be current), looked up once per device.
+int error_word_address(int device, unsigned int** out) {
+    static std::mutex mu;
+    static unsigned int* cache[kMaxDevices];
+    if (device < 0 || device >= kMaxDevices) return NA2D_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[device] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_error_word);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_error_word)");
+        cache[device] = static_cast<unsigned int*>(p);
+    }
+    *out = cache[device];
+    return NA2D_OK;
+}
+
+// The kernel of na2d_selftest_wait_timeout: one thread waits on a barrier nothing completes.
+__global__ void wait_timeout_kernel(unsigned int* err_word, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        na2d_ptx::mbar_init(&bar, 1);
+        na2d_ptx::mbar_fence_init();
+        const na2d_ptx::WaitCtx wctx{&abort_flag, err_word, limit_ns};
+        na2d_ptx::mbar_wait(&bar, 0, wctx, na2d_ptx::kErrOther);
+    }
+}
+
+// ---- problem description --------------------------------------------------------------------------
+struct Tensor {
+    void* ptr = nullptr;
+    Na2dStride st{0, 0, 0, 0};
 };
 
-int make_problem(int B, int N, int H, int W, int C, int ks, int dtype, const na2d_rows* rows,
-                 int path, Problem* out) {
+struct Problem {
+    Na2dGeom g;
+    int B = 0;
+    int dtype = 0;
+    bool tensor = false;      // run the tcgen05 kernels
+    int device = 0;
+    cudaStream_t st = nullptr;
+    Tensor q, k, v, o, d_o, d_q, d_k, d_v;
+    float* lse = nullptr;
+    float* delta = nullptr;
+};
+
+// Strides of one operand: the caller's, or dense (B, N, rows, W, C) when all four are zero.  The
+// stride of a dimension of extent 1 never reaches an address, so whatever the caller passed for
+// it is replaced by the dense value (frameworks report arbitrary strides there).
+Tensor resolve(const na2d_tensor& t, int B, int N, int rows, int W, int C, bool one_d) {
+    Tensor r;
+    r.ptr = t.ptr;
+    const bool dense = t.stride_b == 0 && t.stride_n == 0 && t.stride_h == 0 && t.stride_w == 0;
+    r.st.w = (dense || W == 1) ? C : t.stride_w;
+    r.st.h = (dense || rows == 1 || one_d) ? (long long)W * r.st.w : t.stride_h;
+    r.st.n = (dense || N == 1) ? (long long)rows * r.st.h : t.stride_n;
+    r.st.b = (dense || B == 1) ? (long long)N * r.st.n : t.stride_b;
+    return r;
+}
+
+// What a TMA tensor map needs of an operand: a 16-byte aligned base, strides that are multiples of
+// 16 bytes (8 elements of 16 bits) and below 2^40 bytes.
+bool tma_compatible(const Tensor& t) {
+    if (t.ptr == nullptr) return true;
+    if (reinterpret_cast<uintptr_t>(t.ptr) & 15u) return false;
+    const long long s[4] = {t.st.b, t.st.n, t.st.h, t.st.w};
+    for (long long x : s)
+        if (x <= 0 || (x & 7) != 0 || x >= (1ll << 39)) return false;
+    return true;
+}
+
+int make_problem(const na2d_args* a, Problem* out) {
+    if (!a || a->struct_size < sizeof(na2d_args)) return NA2D_ERR_BAD_ARG;
+    const int B = a->B, N = a->N, H = a->H, W = a->W, C = a->C, ks = a->kernel_size, dtype = a->dtype, path = a->path;
     if (B <= 0 || N <= 0 || H <= 0 || W <= 0 || C <= 0) return NA2D_ERR_BAD_ARG;
     if (ks <= 0 || (ks & 1) == 0) return NA2D_ERR_BAD_ARG;
     if (dtype != NA2D_F32 && dtype != NA2D_BF16 && dtype != NA2D_F16) return NA2D_ERR_UNSUPPORTED;
     if (path != NA2D_PATH_AUTO && path != NA2D_PATH_SIMT && path != NA2D_PATH_TENSOR) return NA2D_ERR_BAD_ARG;
+    if (a->op != NA2D_OP_2D && a->op != NA2D_OP_1D) return NA2D_ERR_BAD_ARG;
+    if (!(a->scale > 0.f) || !(a->scale < 3.0e38f)) return NA2D_ERR_BAD_ARG;
     if ((long long)B * N > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
+    const bool one_d = a->op == NA2D_OP_1D;
     Na2dGeom g;
-    g.BN = B * N; g.W = W; g.C = C; g.ks = ks;
-    if (rows) {
-        g.q_row0 = rows->q_row0; g.Hq = rows->Hq; g.kv_row0 = rows->kv_row0; g.Hkv = rows->Hkv;
-        g.Hg = rows->H_global;
-        if (g.Hq <= 0 || g.Hkv <= 0 || g.Hg <= 0 || g.q_row0 < 0 || g.kv_row0 < 0) return NA2D_ERR_BAD_ARG;
-        if (g.q_row0 + g.Hq > g.Hg || g.kv_row0 + g.Hkv > g.Hg) return NA2D_ERR_BAD_ARG;
+    g.BN = B * N; g.N = N; g.W = W; g.C = C; g.ks = ks; g.kh = one_d ? 1 : ks;
+    g.scale = a->scale;
+    g.sl2 = a->scale * 1.4426950408889634f;
+    if (one_d) {
+        if (H != 1 || a->rows) return NA2D_ERR_BAD_ARG;
+        g.q_row0 = 0; g.Hq = 1; g.kv_row0 = 0; g.Hkv = 1; g.Hg = 1;
+        // the reference reads out of range when the sequence is shorter than the window
+        // (e_natten/pytorch.py:7-11 goes negative); here that is an error
+        if (W < ks) return NA2D_ERR_WINDOW;
     } else {
-        g.q_row0 = 0; g.Hq = H; g.kv_row0 = 0; g.Hkv = H; g.Hg = H;
+        const na2d_rows* rows = a->rows;
+        if (rows) {
+            g.q_row0 = rows->q_row0; g.Hq = rows->Hq; g.kv_row0 = rows->kv_row0; g.Hkv = rows->Hkv;
+            g.Hg = rows->H_global;
+            if (g.Hq <= 0 || g.Hkv <= 0 || g.Hg <= 0 || g.q_row0 < 0 || g.kv_row0 < 0) return NA2D_ERR_BAD_ARG;
+            if (g.q_row0 + g.Hq > g.Hg || g.kv_row0 + g.Hkv > g.Hg) return NA2D_ERR_BAD_ARG;
+        } else {
+            g.q_row0 = 0; g.Hq = H; g.kv_row0 = 0; g.Hkv = H; g.Hg = H;
+        }
+        // The reference silently reads garbage when a grid side is below the kernel size
+        // (e_natten/pytorch.py:7-11 goes negative); here that is an error.
+        if (g.Hg < ks || W < ks) return NA2D_ERR_WINDOW;
+        // the key band must hold every window of the query band
+        if (na2d_ws(g.q_row0, g.Hg, ks) < g.kv_row0) return NA2D_ERR_WINDOW;
+        if (na2d_ws(g.q_row0 + g.Hq - 1, g.Hg, ks) + ks > g.kv_row0 + g.Hkv) return NA2D_ERR_WINDOW;
     }
-    // The reference silently reads garbage when a grid side is below the kernel size
-    // (e_natten/pytorch.py:7-11 goes negative); here that is an error.
-    if (g.Hg < ks || W < ks) return NA2D_ERR_WINDOW;
-    // the key band must hold every window of the query band
-    if (na2d_ws(g.q_row0, g.Hg, ks) < g.kv_row0) return NA2D_ERR_WINDOW;
-    if (na2d_ws(g.q_row0 + g.Hq - 1, g.Hg, ks) + ks > g.kv_row0 + g.Hkv) return NA2D_ERR_WINDOW;
+    Problem& p = *out;
+    p.q = resolve(a->q, B, N, g.Hq, W, C, one_d);
+    p.o = resolve(a->o, B, N, g.Hq, W, C, one_d);
+    p.d_o = resolve(a->d_o, B, N, g.Hq, W, C, one_d);
+    p.d_q = resolve(a->d_q, B, N, g.Hq, W, C, one_d);
+    p.k = resolve(a->k, B, N, g.Hkv, W, C, one_d);
+    p.v = resolve(a->v, B, N, g.Hkv, W, C, one_d);
+    p.d_k = resolve(a->d_k, B, N, g.Hkv, W, C, one_d);
+    p.d_v = resolve(a->d_v, B, N, g.Hkv, W, C, one_d);
 
-    const bool tc_ok = na2d_tc::supported(dtype, C, ks);
+    bool tc_ok = !one_d && na2d_tc::supported(dtype, C, ks);
+    if (tc_ok) {
+        for (const Tensor* t : {&p.q, &p.k, &p.v, &p.o, &p.d_o, &p.d_q, &p.d_k, &p.d_v})
+            tc_ok = tc_ok && tma_compatible(*t);
+    }
     bool tensor = false;
     if (path == NA2D_PATH_TENSOR) {
         if (!tc_ok) return NA2D_ERR_UNSUPPORTED;
@@ -111,60 +214,191 @@ int make_problem(int B, int N, int H, int W, int C, int ks, int dtype, const na2
         tensor = tc_ok;
     }
     if (!tensor && (C > na2d_simt::kMaxC || ks > na2d_simt::kMaxKs)) return NA2D_ERR_UNSUPPORTED;
-    out->g = g; out->dtype = dtype; out->tensor = tensor;
+    p.g = g; p.B = B; p.dtype = dtype; p.tensor = tensor;
+    p.device = a->device; p.st = (cudaStream_t)a->stream;
+    p.lse = a->lse; p.delta = a->delta;
     return NA2D_OK;
 }
 
-long long blocks_for(long long items) { return (items + na2d_simt::kWarps - 1) / na2d_simt::kWarps; }
+// ---- dispatch helpers -------------------------------------------------------------------------------
+template <int V> using IntTag = std::integral_constant<int, V>;
+template <typename T> struct TypeTag { using type = T; };
 
-template <typename T>
-int simt_forward(const Problem& p, const void* q, const void* k, const void* v, void* o, float* lse,
-                 cudaStream_t st) {
-    const Na2dGeom& g = p.g;
-    const long long nq = (long long)g.BN * g.Hq * g.W;
-    const long long nb = blocks_for(nq);
+// Calls f(TypeTag<element type>, IntTag<channels per lane>) for the problem's dtype and head dim.
+template <typename F>
+int simt_dispatch(int dtype, int C, F&& f) {
+    auto by_cpl = [&](auto type_tag) -> int {
+        if (C <= 32) return f(type_tag, IntTag<1>{});
+        if (C <= 64) return f(type_tag, IntTag<2>{});
+        if (C <= 128) return f(type_tag, IntTag<4>{});
+        return f(type_tag, IntTag<8>{});
+    };
+    switch (dtype) {
+        case NA2D_F32: return by_cpl(TypeTag<float>{});
+        case NA2D_BF16: return by_cpl(TypeTag<__nv_bfloat16>{});
+        default: return by_cpl(TypeTag<__half>{});
+    }
+}
+
+// One block per patch of a (BN, H, W) pixel grid.
+int grid_for(long long BN, int H, int W, unsigned* grid) {
+    const long long nb = na2d_simt::patch_count(BN, H, W);
     if (nb > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
-    const size_t smem = na2d_simt::fwd_smem_bytes(g.C, g.ks);
-    na2d_simt::fwd_kernel<T><<<(unsigned)nb, na2d_simt::kWarps * 32, smem, st>>>(
-        (const T*)q, (const T*)k, (const T*)v, (T*)o, lse, g);
+    *grid = (unsigned)nb;
+    return NA2D_OK;
+}
+
+constexpr int kSimtThreads = na2d_simt::kWarps * 32;
+
+int after_launch() {
     g_launches.fetch_add(1);
     NA2D_CUDA(cudaGetLastError());
     return NA2D_OK;
 }
 
-template <typename T>
-int simt_backward_dq(const Problem& p, const void* q, const void* k, const void* v,
-                     const float* lse, const void* d_o, void* d_q, float* delta, cudaStream_t st) {
-    const Na2dGeom& g = p.g;
-    const long long nq = (long long)g.BN * g.Hq * g.W;
-    if (blocks_for(nq) > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
-    na2d_simt::dq_kernel<T><<<(unsigned)blocks_for(nq), na2d_simt::kWarps * 32,
-                              na2d_simt::dq_smem_bytes(g.C, g.ks), st>>>(
-        (const T*)q, (const T*)k, (const T*)v, lse, (const T*)d_o, (T*)d_q, delta, g);
-    g_launches.fetch_add(1);
-    NA2D_CUDA(cudaGetLastError());
+na2d_tc::TensorArg targ(const Tensor& t) { return na2d_tc::TensorArg{t.ptr, t.st}; }
+
+int launch_ctx(const Problem& p, int* launched, na2d_tc::LaunchCtx* lc) {
+    unsigned int* err = nullptr;
+    int rc = error_word_address(p.device, &err);
+    if (rc != NA2D_OK) return rc;
+    *lc = na2d_tc::LaunchCtx{p.g, p.dtype, p.B, p.device, p.st, err, launched};
     return NA2D_OK;
 }
 
-template <typename T>
-int simt_backward_dkdv(const Problem& p, const void* q, const void* k, const void* v, const float* lse,
-                       const void* d_o, const float* delta, void* d_k, void* d_v, cudaStream_t st) {
+// ---- the three compute steps ---------------------------------------------------------------------------
+int run_forward(const Problem& p) {
     const Na2dGeom& g = p.g;
-    const long long nkey = (long long)g.BN * g.Hkv * g.W;
-    if (blocks_for(nkey) > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
-    na2d_simt::dkdv_kernel<T><<<(unsigned)blocks_for(nkey), na2d_simt::kWarps * 32,
-                                na2d_simt::dkdv_smem_bytes(g.C), st>>>(
-        (const T*)q, (const T*)k, (const T*)v, lse, (const T*)d_o, delta, (T*)d_k, (T*)d_v, g);
-    g_launches.fetch_add(1);
-    NA2D_CUDA(cudaGetLastError());
-    return NA2D_OK;
+    if (p.tensor) {
+        int launched = 0;
+        na2d_tc::LaunchCtx lc;
+        int rc = launch_ctx(p, &launched, &lc);
+        if (rc != NA2D_OK) return rc;
+        rc = p.dtype == NA2D_BF16 ? na2d_tc::forward_bf16(lc, targ(p.q), targ(p.k), targ(p.v), targ(p.o), p.lse)
+                                  : na2d_tc::forward_f16(lc, targ(p.q), targ(p.k), targ(p.v), targ(p.o), p.lse);
+        g_launches.fetch_add(launched);
+        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 forward launch");
+        return rc;
+    }
+    unsigned grid = 0;
+    int rc = grid_for(g.BN, g.Hq, g.W, &grid);
+    if (rc != NA2D_OK) return rc;
+    return simt_dispatch(p.dtype, g.C, [&](auto tt, auto cpl) -> int {
+        using T = typename decltype(tt)::type;
+        na2d_simt::fwd_kernel<T, decltype(cpl)::value>
+            <<<grid, kSimtThreads, na2d_simt::window_smem_bytes(g.kh, g.ks, 1), p.st>>>(
+                (const T*)p.q.ptr, (const T*)p.k.ptr, (const T*)p.v.ptr, (T*)p.o.ptr, p.lse, p.q.st, p.k.st, p.v.st,
+                p.o.st, g);
+        return after_launch();
+    });
+}
+
+int run_backward_dq(const Problem& p) {
+    const Na2dGeom& g = p.g;
+    if (p.tensor) {
+        int launched = 0;
+        na2d_tc::LaunchCtx lc;
+        int rc = launch_ctx(p, &launched, &lc);
+        if (rc != NA2D_OK) return rc;
+        // With the forward's output at hand, the dQ kernel of the larger windows gets an estimate of
+        // the row deltas (dO . o) and walks its key box once; it overwrites the estimate with the
+        // exact deltas.
+        const float* delta_in = nullptr;
+        if (g.ks >= 7 && p.o.ptr && p.d_q.ptr) {
+            const long long nq = (long long)g.BN * g.Hq * g.W;
+            const long long nb = (nq + na2d_delta::kWarps - 1) / na2d_delta::kWarps;
+            if (nb > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
+            const unsigned grid = (unsigned)nb;
+            if (p.dtype == NA2D_BF16)
+                na2d_delta::delta_kernel<__nv_bfloat16><<<grid, na2d_delta::kWarps * 32, 0, p.st>>>(
+                    (const __nv_bfloat16*)p.d_o.ptr, (const __nv_bfloat16*)p.o.ptr, p.delta, p.d_o.st, p.o.st, g);
+            else
+                na2d_delta::delta_kernel<__half><<<grid, na2d_delta::kWarps * 32, 0, p.st>>>(
+                    (const __half*)p.d_o.ptr, (const __half*)p.o.ptr, p.delta, p.d_o.st, p.o.st, g);
+            rc = after_launch();
+            if (rc != NA2D_OK) return rc;
+            delta_in = p.delta;
+        }
+        rc = p.dtype == NA2D_BF16
+                 ? na2d_tc::backward_dq_bf16(lc, targ(p.q), targ(p.k), targ(p.v), p.lse, targ(p.d_o), targ(p.d_q), p.delta, delta_in)
+                 : na2d_tc::backward_dq_f16(lc, targ(p.q), targ(p.k), targ(p.v), p.lse, targ(p.d_o), targ(p.d_q), p.delta, delta_in);
+        g_launches.fetch_add(launched);
+        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 dQ launch");
+        return rc;
+    }
+    unsigned grid = 0;
+    int rc = grid_for(g.BN, g.Hq, g.W, &grid);
+    if (rc != NA2D_OK) return rc;
+    return simt_dispatch(p.dtype, g.C, [&](auto tt, auto cpl) -> int {
+        using T = typename decltype(tt)::type;
+        na2d_simt::dq_kernel<T, decltype(cpl)::value>
+            <<<grid, kSimtThreads, na2d_simt::window_smem_bytes(g.kh, g.ks, 2), p.st>>>(
+                (const T*)p.q.ptr, (const T*)p.k.ptr, (const T*)p.v.ptr, p.lse, (const T*)p.d_o.ptr, (T*)p.d_q.ptr,
+                p.delta, p.q.st, p.k.st, p.v.st, p.d_o.st, p.d_q.st, g);
+        return after_launch();
+    });
+}
+
+int run_backward_dkdv(const Problem& p) {
+    const Na2dGeom& g = p.g;
+    if (p.tensor) {
+        int launched = 0;
+        na2d_tc::LaunchCtx lc;
+        int rc = launch_ctx(p, &launched, &lc);
+        if (rc != NA2D_OK) return rc;
+        rc = p.dtype == NA2D_BF16
+                 ? na2d_tc::backward_dkdv_bf16(lc, targ(p.q), targ(p.k), targ(p.v), p.lse, targ(p.d_o), p.delta, targ(p.d_k), targ(p.d_v))
+                 : na2d_tc::backward_dkdv_f16(lc, targ(p.q), targ(p.k), targ(p.v), p.lse, targ(p.d_o), p.delta, targ(p.d_k), targ(p.d_v));
+        g_launches.fetch_add(launched);
+        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 dK/dV launch");
+        return rc;
+    }
+    unsigned grid = 0;
+    int rc = grid_for(g.BN, g.Hkv, g.W, &grid);
+    if (rc != NA2D_OK) return rc;
+    return simt_dispatch(p.dtype, g.C, [&](auto tt, auto cpl) -> int {
+        using T = typename decltype(tt)::type;
+        na2d_simt::dkdv_kernel<T, decltype(cpl)::value><<<grid, kSimtThreads, 0, p.st>>>(
+            (const T*)p.q.ptr, (const T*)p.k.ptr, (const T*)p.v.ptr, p.lse, (const T*)p.d_o.ptr, p.delta,
+            (T*)p.d_k.ptr, (T*)p.d_v.ptr, p.q.st, p.k.st, p.v.st, p.d_o.st, p.d_k.st, p.d_v.st, g);
+        return after_launch();
+    });
+}
+
+// Validate, select the device, check it; then run `step`.
+template <typename F>
+int enter(const na2d_args* a, F&& step) {
+    Problem p;
+    int rc = make_problem(a, &p);
+    if (rc != NA2D_OK) return rc;
+    DeviceScope scope(p.device);
+    if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");
+    rc = check_device(p.device);
+    if (rc != NA2D_OK) return rc;
+    return step(p);
+}
+
+na2d_tensor dense(const void* ptr) { return na2d_tensor{const_cast<void*>(ptr), 0, 0, 0, 0}; }
+
+na2d_args dense_args(int op, int B, int N, int H, int W, int C, int ks, int dtype, const na2d_rows* rows, int path,
+                     int device, void* stream) {
+    na2d_args a;
+    std::memset(&a, 0, sizeof(a));
+    a.struct_size = sizeof(a);
+    a.op = op;
+    a.B = B; a.N = N; a.H = H; a.W = W; a.C = C; a.kernel_size = ks; a.dtype = dtype; a.path = path; a.device = device;
+    a.scale = 1.f;
+    a.stream = stream;
+    a.rows = rows;
+    return a;
 }
 
 // ---- scratch for na2d_backward_static_scratch ----------------------------------------------------
 // The backward pair passes the row delta from the dQ kernel to the dK/dV kernel through global
 // memory.  Normally the caller provides that buffer; the entry point below keeps it in this
 // file-scope device array instead, so that a caller who may not allocate can still run the
-// backward.  Every GPU that loads the library carries the array (4 MiB) until the process exits.
+// backward.  Every GPU on which the library's device code has been loaded carries the array
+// (4 MiB) until the process exits.
 constexpr long long kStaticDeltaFloats = 1LL << 20;
 static __device__ __align__(256) float g_static_delta[kStaticDeltaFloats];
 
@@ -173,8 +407,8 @@ static __device__ __align__(256) float g_static_delta[kStaticDeltaFloats];
 // address comes from cudaGetSymbolAddress, asked while `device` is the current device.
 int static_delta_address(int device, float** out) {
     static std::mutex mu;
-    static float* cache[64];
-    if (device < 0 || device >= 64) return NA2D_ERR_BAD_ARG;
+    static float* cache[kMaxDevices];
+    if (device < 0 || device >= kMaxDevices) return NA2D_ERR_BAD_ARG;
     std::lock_guard<std::mutex> lock(mu);
     if (cache[device] == nullptr) {
         void* p = nullptr;
@@ -186,28 +420,101 @@ int static_delta_address(int device, float** out) {
     return NA2D_OK;
 }
 
-// Common prologue of the compute entry points: validate, select the device, check it.
-#define NA2D_ENTER()                                                                      \
-    Problem p;                                                                            \
-    int rc = make_problem(B, N, H, W, C, kernel_size, dtype, rows, path, &p);             \
-    if (rc != NA2D_OK) return rc;                                                         \
-    DeviceScope scope(device);                                                            \
-    if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");           \
-    rc = check_device(device);                                                            \
-    if (rc != NA2D_OK) return rc;                                                         \
-    cudaStream_t st = (cudaStream_t)stream;
+// ---- the unfused pair -------------------------------------------------------------------------------------
+struct PairProblem {
+    Na2dGeom g;
+    int dtype;
+    Na2dStride st;          // dense strides of a (B, N, H, W, C) tensor
+    cudaStream_t stream;
+};
+
+int make_pair_problem(int B, int N, int H, int W, int C, int ks, int dtype, void* stream, PairProblem* out) {
+    if (B <= 0 || N <= 0 || H <= 0 || W <= 0 || C <= 0) return NA2D_ERR_BAD_ARG;
+    if (ks <= 0 || (ks & 1) == 0) return NA2D_ERR_BAD_ARG;
+    if (dtype != NA2D_F32 && dtype != NA2D_BF16 && dtype != NA2D_F16) return NA2D_ERR_UNSUPPORTED;
+    if ((long long)B * N > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
+    if (H < ks || W < ks) return NA2D_ERR_WINDOW;
+    if (C > na2d_simt::kMaxC || ks > na2d_simt::kMaxKs) return NA2D_ERR_UNSUPPORTED;
+    Na2dGeom g;
+    g.BN = B * N; g.N = N; g.Hq = H; g.Hkv = H; g.W = W; g.C = C; g.ks = ks; g.kh = ks;
+    g.q_row0 = 0; g.kv_row0 = 0; g.Hg = H; g.scale = 1.f; g.sl2 = 1.4426950408889634f;
+    out->g = g;
+    out->dtype = dtype;
+    out->st = Na2dStride{(long long)N * H * W * C, (long long)H * W * C, (long long)W * C, C};
+    out->stream = (cudaStream_t)stream;
+    return NA2D_OK;
+}
+
+template <typename F>
+int enter_pair(int B, int N, int H, int W, int C, int ks, int dtype, int device, void* stream, F&& step) {
+    PairProblem p;
+    int rc = make_pair_problem(B, N, H, W, C, ks, dtype, stream, &p);
+    if (rc != NA2D_OK) return rc;
+    DeviceScope scope(device);
+    if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");
+    rc = check_device(device);
+    if (rc != NA2D_OK) return rc;
+    return step(p);
+}
+
+// x . y over the window -> attn
+int pair_dot(const PairProblem& p, const void* x, const void* y, void* attn) {
+    unsigned grid = 0;
+    int rc = grid_for(p.g.BN, p.g.Hq, p.g.W, &grid);
+    if (rc != NA2D_OK) return rc;
+    return simt_dispatch(p.dtype, p.g.C, [&](auto tt, auto cpl) -> int {
+        using T = typename decltype(tt)::type;
+        na2d_simt::window_dot_kernel<T, decltype(cpl)::value><<<grid, kSimtThreads, 0, p.stream>>>(
+            (const T*)x, (const T*)y, (T*)attn, p.st, p.st, p.g);
+        return after_launch();
+    });
+}
+// sum_j attn_j y_j -> out
+int pair_apply(const PairProblem& p, const void* attn, const void* y, void* out) {
+    unsigned grid = 0;
+    int rc = grid_for(p.g.BN, p.g.Hq, p.g.W, &grid);
+    if (rc != NA2D_OK) return rc;
+    return simt_dispatch(p.dtype, p.g.C, [&](auto tt, auto cpl) -> int {
+        using T = typename decltype(tt)::type;
+        na2d_simt::window_apply_kernel<T, decltype(cpl)::value>
+            <<<grid, kSimtThreads, na2d_simt::window_smem_bytes(p.g.kh, p.g.ks, 1), p.stream>>>(
+                (const T*)attn, (const T*)y, (T*)out, p.st, p.st, p.g);
+        return after_launch();
+    });
+}
+// key-side sum over the inverse neighbourhood of attn x -> out
+int pair_inverse(const PairProblem& p, const void* attn, const void* x, void* out) {
+    unsigned grid = 0;
+    int rc = grid_for(p.g.BN, p.g.Hkv, p.g.W, &grid);
+    if (rc != NA2D_OK) return rc;
+    return simt_dispatch(p.dtype, p.g.C, [&](auto tt, auto cpl) -> int {
+        using T = typename decltype(tt)::type;
+        na2d_simt::window_inverse_kernel<T, decltype(cpl)::value><<<grid, kSimtThreads, 0, p.stream>>>(
+            (const T*)attn, (const T*)x, (T*)out, p.st, p.st, p.g);
+        return after_launch();
+    });
+}
+
+// ---- na2d_poll state -----------------------------------------------------------------------------------------
+struct PollState {
+    unsigned int* host = nullptr;     // pinned
+    cudaEvent_t ev = nullptr;
+    bool pending = false;
+};
+std::mutex g_poll_mu;
+PollState g_poll[kMaxDevices];
 
 }  // namespace
 
 extern "C" {
 
-int na2d_version(void) { return 100; }
+int na2d_version(void) { return 200; }
 
 const char* na2d_strerror(int status) {
     switch (status) {
         case NA2D_OK: return "ok";
-        case NA2D_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size, even kernel size or bad row view)";
-        case NA2D_ERR_UNSUPPORTED: return "unsupported dtype, head dim or kernel size for the requested path";
+        case NA2D_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size, even kernel size, bad scale or bad row view)";
+        case NA2D_ERR_UNSUPPORTED: return "unsupported dtype, head dim, kernel size or tensor layout for the requested path";
         case NA2D_ERR_WINDOW: return "grid side smaller than the kernel size, or key band does not cover the query band's windows";
         case NA2D_ERR_CUDA: return "CUDA call failed (see na2d_last_cuda_error)";
         case NA2D_ERR_NO_DEVICE: return "device is not an sm_100 (B200) GPU";
@@ -235,83 +542,124 @@ int na2d_dump_index(int32_t* ws, int32_t* bws, int32_t* bwe, int seq_len, int ke
     if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");
     na2d_simt::index_dump_kernel<<<(seq_len + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
         ws, bws, bwe, seq_len, kernel_size);
-    g_launches.fetch_add(1);
-    NA2D_CUDA(cudaGetLastError());
-    return NA2D_OK;
+    return after_launch();
 }
 
+// ---- strided / scaled / 1D entry points ------------------------------------------------------------------
+int na2d_forward_ex(const na2d_args* a) {
+    if (!a || !a->q.ptr || !a->k.ptr || !a->v.ptr || !a->o.ptr || !a->lse) return NA2D_ERR_BAD_ARG;
+    return enter(a, [](const Problem& p) { return run_forward(p); });
+}
+
+int na2d_backward_dq_ex(const na2d_args* a) {
+    if (!a || !a->q.ptr || !a->k.ptr || !a->v.ptr || !a->lse || !a->d_o.ptr || !a->delta) return NA2D_ERR_BAD_ARG;
+    return enter(a, [](const Problem& p) { return run_backward_dq(p); });
+}
+
+int na2d_backward_dkdv_ex(const na2d_args* a) {
+    if (!a || !a->q.ptr || !a->k.ptr || !a->v.ptr || !a->lse || !a->d_o.ptr || !a->delta || !a->d_k.ptr || !a->d_v.ptr)
+        return NA2D_ERR_BAD_ARG;
+    return enter(a, [](const Problem& p) { return run_backward_dkdv(p); });
+}
+
+int na2d_backward_ex(const na2d_args* a) {
+    if (!a) return NA2D_ERR_BAD_ARG;
+    if ((a->d_k.ptr == nullptr) != (a->d_v.ptr == nullptr)) return NA2D_ERR_BAD_ARG;
+    if (!a->d_q.ptr && !a->d_k.ptr) return NA2D_ERR_BAD_ARG;
+    // the query half always runs: it produces delta, which the key half needs
+    int rc = na2d_backward_dq_ex(a);
+    if (rc != NA2D_OK || a->d_k.ptr == nullptr) return rc;
+    return na2d_backward_dkdv_ex(a);
+}
+
+// ---- dense entry points -------------------------------------------------------------------------------------
 int na2d_forward(const void* q, const void* k, const void* v, void* o, float* lse,
                  int B, int N, int H, int W, int C, int kernel_size, int dtype,
                  const na2d_rows* rows, int path, int device, void* stream) {
-    if (!q || !k || !v || !o || !lse) return NA2D_ERR_BAD_ARG;
-    NA2D_ENTER();
-    if (p.tensor) {
-        int launched = 0;
-        rc = na2d_tc::forward(p.g, dtype, q, k, v, o, lse, device, st, &launched);
-        g_launches.fetch_add(launched);
-        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 forward launch");
-        return rc;
-    }
-    switch (dtype) {
-        case NA2D_F32: return simt_forward<float>(p, q, k, v, o, lse, st);
-        case NA2D_BF16: return simt_forward<__nv_bfloat16>(p, q, k, v, o, lse, st);
-        default: return simt_forward<__half>(p, q, k, v, o, lse, st);
-    }
+    na2d_args a = dense_args(NA2D_OP_2D, B, N, H, W, C, kernel_size, dtype, rows, path, device, stream);
+    a.q = dense(q); a.k = dense(k); a.v = dense(v); a.o = dense(o); a.lse = lse;
+    return na2d_forward_ex(&a);
 }
 
 int na2d_backward_dq(const void* q, const void* k, const void* v, const void* o, const float* lse,
                      const void* d_o, void* d_q, float* delta,
                      int B, int N, int H, int W, int C, int kernel_size, int dtype,
                      const na2d_rows* rows, int path, int device, void* stream) {
-    (void)o;   // not read: delta is formed as sum_j p_j dp_j, see the header
-    if (!q || !k || !v || !lse || !d_o || !delta) return NA2D_ERR_BAD_ARG;
-    NA2D_ENTER();
-    if (p.tensor) {
-        int launched = 0;
-        rc = na2d_tc::backward_dq(p.g, dtype, q, k, v, o, lse, d_o, d_q, delta, device, st, &launched);
-        g_launches.fetch_add(launched);
-        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 dQ launch");
-        return rc;
-    }
-    switch (dtype) {
-        case NA2D_F32: return simt_backward_dq<float>(p, q, k, v, lse, d_o, d_q, delta, st);
-        case NA2D_BF16: return simt_backward_dq<__nv_bfloat16>(p, q, k, v, lse, d_o, d_q, delta, st);
-        default: return simt_backward_dq<__half>(p, q, k, v, lse, d_o, d_q, delta, st);
-    }
+    na2d_args a = dense_args(NA2D_OP_2D, B, N, H, W, C, kernel_size, dtype, rows, path, device, stream);
+    a.q = dense(q); a.k = dense(k); a.v = dense(v); a.o = dense(o); a.lse = const_cast<float*>(lse);
+    a.d_o = dense(d_o); a.d_q = dense(d_q); a.delta = delta;
+    return na2d_backward_dq_ex(&a);
 }
 
 int na2d_backward_dkdv(const void* q, const void* k, const void* v, const float* lse,
                        const void* d_o, const float* delta, void* d_k, void* d_v,
                        int B, int N, int H, int W, int C, int kernel_size, int dtype,
                        const na2d_rows* rows, int path, int device, void* stream) {
-    if (!q || !k || !v || !lse || !d_o || !delta || !d_k || !d_v) return NA2D_ERR_BAD_ARG;
-    NA2D_ENTER();
-    if (p.tensor) {
-        int launched = 0;
-        rc = na2d_tc::backward_dkdv(p.g, dtype, q, k, v, lse, d_o, delta, d_k, d_v, device, st, &launched);
-        g_launches.fetch_add(launched);
-        if (rc == NA2D_ERR_CUDA) return tc_fail("tcgen05 dK/dV launch");
-        return rc;
-    }
-    switch (dtype) {
-        case NA2D_F32: return simt_backward_dkdv<float>(p, q, k, v, lse, d_o, delta, d_k, d_v, st);
-        case NA2D_BF16: return simt_backward_dkdv<__nv_bfloat16>(p, q, k, v, lse, d_o, delta, d_k, d_v, st);
-        default: return simt_backward_dkdv<__half>(p, q, k, v, lse, d_o, delta, d_k, d_v, st);
-    }
+    na2d_args a = dense_args(NA2D_OP_2D, B, N, H, W, C, kernel_size, dtype, rows, path, device, stream);
+    a.q = dense(q); a.k = dense(k); a.v = dense(v); a.lse = const_cast<float*>(lse);
+    a.d_o = dense(d_o); a.delta = const_cast<float*>(delta); a.d_k = dense(d_k); a.d_v = dense(d_v);
+    return na2d_backward_dkdv_ex(&a);
 }
 
 int na2d_backward(const void* q, const void* k, const void* v, const void* o, const float* lse,
                   const void* d_o, void* d_q, void* d_k, void* d_v, float* delta,
                   int B, int N, int H, int W, int C, int kernel_size, int dtype,
                   const na2d_rows* rows, int path, int device, void* stream) {
-    if ((d_k == nullptr) != (d_v == nullptr)) return NA2D_ERR_BAD_ARG;
-    if (!d_q && !d_k) return NA2D_ERR_BAD_ARG;
-    // the query half always runs: it produces delta, which the key half needs
-    int rc = na2d_backward_dq(q, k, v, o, lse, d_o, d_q, delta, B, N, H, W, C, kernel_size, dtype,
-                              rows, path, device, stream);
-    if (rc != NA2D_OK || d_k == nullptr) return rc;
-    return na2d_backward_dkdv(q, k, v, lse, d_o, delta, d_k, d_v, B, N, H, W, C, kernel_size, dtype,
-                              rows, path, device, stream);
+    na2d_args a = dense_args(NA2D_OP_2D, B, N, H, W, C, kernel_size, dtype, rows, path, device, stream);
+    a.q = dense(q); a.k = dense(k); a.v = dense(v); a.o = dense(o); a.lse = const_cast<float*>(lse);
+    a.d_o = dense(d_o); a.d_q = dense(d_q); a.d_k = dense(d_k); a.d_v = dense(d_v); a.delta = delta;
+    return na2d_backward_ex(&a);
+}
+
+int na1d_forward(const void* q, const void* k, const void* v, void* o, float* lse,
+                 int B, int N, int T, int C, int kernel_size, int dtype, int device, void* stream) {
+    na2d_args a = dense_args(NA2D_OP_1D, B, N, 1, T, C, kernel_size, dtype, nullptr, NA2D_PATH_AUTO, device, stream);
+    a.q = dense(q); a.k = dense(k); a.v = dense(v); a.o = dense(o); a.lse = lse;
+    return na2d_forward_ex(&a);
+}
+
+int na1d_backward(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                  const void* d_o, void* d_q, void* d_k, void* d_v, float* delta,
+                  int B, int N, int T, int C, int kernel_size, int dtype, int device, void* stream) {
+    na2d_args a = dense_args(NA2D_OP_1D, B, N, 1, T, C, kernel_size, dtype, nullptr, NA2D_PATH_AUTO, device, stream);
+    a.q = dense(q); a.k = dense(k); a.v = dense(v); a.o = dense(o); a.lse = const_cast<float*>(lse);
+    a.d_o = dense(d_o); a.d_q = dense(d_q); a.d_k = dense(d_k); a.d_v = dense(d_v); a.delta = delta;
+    return na2d_backward_ex(&a);
+}
+
+// ---- the unfused pair -------------------------------------------------------------------------------------------
+int na2d_qk_forward(const void* q, const void* k, void* attn,
+                    int B, int N, int H, int W, int C, int kernel_size, int dtype, int device, void* stream) {
+    if (!q || !k || !attn) return NA2D_ERR_BAD_ARG;
+    return enter_pair(B, N, H, W, C, kernel_size, dtype, device, stream,
+                      [&](const PairProblem& p) { return pair_dot(p, q, k, attn); });
+}
+
+int na2d_qk_backward(const void* q, const void* k, const void* d_attn, void* d_q, void* d_k,
+                     int B, int N, int H, int W, int C, int kernel_size, int dtype, int device, void* stream) {
+    if (!q || !k || !d_attn || !d_q || !d_k) return NA2D_ERR_BAD_ARG;
+    return enter_pair(B, N, H, W, C, kernel_size, dtype, device, stream, [&](const PairProblem& p) {
+        int rc = pair_apply(p, d_attn, k, d_q);
+        if (rc != NA2D_OK) return rc;
+        return pair_inverse(p, d_attn, q, d_k);
+    });
+}
+
+int na2d_av_forward(const void* attn, const void* v, void* out,
+                    int B, int N, int H, int W, int C, int kernel_size, int dtype, int device, void* stream) {
+    if (!attn || !v || !out) return NA2D_ERR_BAD_ARG;
+    return enter_pair(B, N, H, W, C, kernel_size, dtype, device, stream,
+                      [&](const PairProblem& p) { return pair_apply(p, attn, v, out); });
+}
+
+int na2d_av_backward(const void* attn, const void* v, const void* d_out, void* d_attn, void* d_v,
+                     int B, int N, int H, int W, int C, int kernel_size, int dtype, int device, void* stream) {
+    if (!attn || !v || !d_out || !d_attn || !d_v) return NA2D_ERR_BAD_ARG;
+    return enter_pair(B, N, H, W, C, kernel_size, dtype, device, stream, [&](const PairProblem& p) {
+        int rc = pair_dot(p, d_out, v, d_attn);
+        if (rc != NA2D_OK) return rc;
+        return pair_inverse(p, attn, d_out, d_v);
+    });
 }
 
 int na2d_backward_static_scratch(const void* q, const void* k, const void* v, const void* o, const float* lse,
@@ -343,10 +691,66 @@ int na2d_backward_static_scratch(const void* q, const void* k, const void* v, co
 int na2d_check(int device, void* stream) {
     DeviceScope scope(device);
     if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");
+    unsigned int* addr = nullptr;
+    int rc = error_word_address(device, &addr);
+    if (rc != NA2D_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
     unsigned int word = 0;
-    int rc = na2d_tc::read_and_clear_error(&word, (cudaStream_t)stream);
-    if (rc != NA2D_OK) return cuda_fail(cudaGetLastError(), "error word readback");
-    return word == 0 ? NA2D_OK : NA2D_ERR_KERNEL_WAIT;
+    NA2D_CUDA(cudaMemcpyAsync(&word, addr, sizeof(word), cudaMemcpyDeviceToHost, st));
+    NA2D_CUDA(cudaStreamSynchronize(st));
+    if (word != 0) {
+        NA2D_CUDA(cudaMemsetAsync(addr, 0, sizeof(word), st));
+        NA2D_CUDA(cudaStreamSynchronize(st));
+        return NA2D_ERR_KERNEL_WAIT;
+    }
+    return NA2D_OK;
+}
+
+int na2d_poll(int device, void* stream) {
+    if (device < 0 || device >= kMaxDevices) return NA2D_ERR_BAD_ARG;
+    DeviceScope scope(device);
+    if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");
+    unsigned int* addr = nullptr;
+    int rc = error_word_address(device, &addr);
+    if (rc != NA2D_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    std::lock_guard<std::mutex> lock(g_poll_mu);
+    PollState& ps = g_poll[device];
+    if (ps.host == nullptr) {
+        void* h = nullptr;
+        NA2D_CUDA(cudaHostAlloc(&h, sizeof(unsigned int), cudaHostAllocDefault));
+        ps.host = static_cast<unsigned int*>(h);
+        *ps.host = 0;
+        NA2D_CUDA(cudaEventCreateWithFlags(&ps.ev, cudaEventDisableTiming));
+    }
+    int result = NA2D_OK;
+    if (ps.pending) {
+        cudaError_t e = cudaEventQuery(ps.ev);
+        if (e == cudaErrorNotReady) return NA2D_OK;           // the previous copy is still on its way
+        if (e != cudaSuccess) return cuda_fail(e, "cudaEventQuery");
+        ps.pending = false;
+        if (*ps.host != 0) {
+            result = NA2D_ERR_KERNEL_WAIT;
+            NA2D_CUDA(cudaMemsetAsync(addr, 0, sizeof(unsigned int), st));
+        }
+    }
+    NA2D_CUDA(cudaMemcpyAsync(ps.host, addr, sizeof(unsigned int), cudaMemcpyDeviceToHost, st));
+    NA2D_CUDA(cudaEventRecord(ps.ev, st));
+    ps.pending = true;
+    return result;
+}
+
+int na2d_selftest_wait_timeout(int device, void* stream, unsigned int limit_us) {
+    DeviceScope scope(device);
+    if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");
+    int rc = check_device(device);
+    if (rc != NA2D_OK) return rc;
+    if (limit_us == 0 || limit_us > 1000000u) return NA2D_ERR_BAD_ARG;       // at most a second
+    unsigned int* addr = nullptr;
+    rc = error_word_address(device, &addr);
+    if (rc != NA2D_OK) return rc;
+    wait_timeout_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(addr, (unsigned long long)limit_us * 1000ull);
+    return after_launch();
 }
 
 long long na2d_launch_count(void) { return g_launches.load(); }

@@ -35,12 +35,21 @@ NA2D_HD int na2d_bwe(int j, int seq_len, int kernel_size) {
 // Geometry of one call, passed by value to every kernel.
 struct Na2dGeom {
     int BN;        // batch * heads
+    int N;         // heads (a unit index bn is batch bn / N, head bn % N)
     int Hq;        // query-side rows held
     int Hkv;       // key-side rows held
     int W;         // grid columns
     int C;         // head dim
-    int ks;        // kernel size (odd)
+    int ks;        // kernel size (odd); the window is kh x ks
+    int kh;        // window rows: ks for the 2D operator, 1 for the 1D operator (a one-row image)
     int q_row0;    // global row of query-side row 0
     int kv_row0;   // global row of key-side row 0
     int Hg;        // rows of the whole image
+    float scale;   // softmax scale: the logits are scale * (q . k)
+    float sl2;     // scale * log2(e)
+};
+
+// Element strides of one (batch, heads, rows, columns, channels) tensor; the channel stride is 1.
+struct Na2dStride {
+    long long b, n, h, w;
 };

@@ -3,16 +3,13 @@
 //
 // Every wait is bounded: when the limit runs out the waiter records a code in the device error
 // word, raises the CTA-wide abort flag and carries on, so that a kernel can never spin for ever;
-// the host reads the word with na2d_check().
+// the host reads the word with na2d_check() or na2d_poll().
 #pragma once
 
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace na2d_ptx {
-
-// Device error word (one per loaded library per device); bits say which wait gave up.
-__device__ unsigned int g_error_word = 0;
 
 enum : unsigned int {
     kErrLoadWait = 1u,      // a TMA load barrier did not complete
@@ -23,10 +20,31 @@ enum : unsigned int {
 // A waiting thread is suspended by the hardware inside mbarrier.try_wait for up to kWaitHintNs
 // (a hint; the hardware may return earlier), so that waiting warps leave the issue slots of their
 // SM sub-partition to the warps that work (the MMA-issue warp shares its scheduler with softmax
-// warps).  kSpinLimit rounds of it bound a wait to about a second.
+// warps).
+// A wait is bounded twice: by the time on the GPU's nanosecond timer (kWaitLimitNs, what ends a
+// wait in practice) and by a count of try_wait rounds (kSpinLimit, a backstop should the timer
+// not advance).  The time bound is what matters under a profiler: a replay pass that instruments
+// the kernel runs the working warps orders of magnitude slower, and a bound counted in rounds
+// alone (as it once was) ran out there although nothing was stuck.
 constexpr uint32_t kWaitHintNs = 1000;
-constexpr uint32_t kSpinLimit = 1u << 20;        // try_wait rounds before giving up
+constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s
+constexpr uint32_t kSpinLimit = 1u << 30;        // try_wait rounds, backstop only
 constexpr uint32_t kSpinLimitAborted = 1u << 8;  // once the CTA has aborted, later waits are short
+
+// What a bounded wait needs to report that it gave up: the CTA-shared abort flag (set by the
+// first waiter that gives up, it shortens every later wait of the CTA), the device error word
+// the host reads with na2d_check / na2d_poll, and the time limit of one wait.
+struct WaitCtx {
+    volatile uint32_t* abort_flag;
+    unsigned int* err_word;
+    unsigned long long limit_ns;
+};
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -73,20 +91,59 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Bounded wait.  `abort_flag` is a CTA-shared word: set by the first waiter that gives up, it
-// shortens every later wait of the CTA.  Returns false if the wait gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          unsigned int err_code) {
-    if (mbar_try_wait(bar, parity)) return true;              // common case: already complete
-    const uint32_t limit = (*abort_flag != 0) ? kSpinLimitAborted : kSpinLimit;
+// Bounded wait.  Returns false if the wait gave up (after recording `err_code`).  The timer is
+// not touched during the first kTimerAfter rounds: nearly every wait ends within a few rounds,
+// and reading the global timer costs more than the rounds it would guard.
+constexpr uint32_t kTimerAfter = 1024;
+__device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const WaitCtx wc, unsigned int err_code) {
+    const bool aborted = *wc.abort_flag != 0;
+    const uint32_t limit = aborted ? kSpinLimitAborted : kSpinLimit;
+    unsigned long long t0 = 0;
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 4096) __nanosleep(32);
+        if (i >= kTimerAfter) {
+            if (i == kTimerAfter) t0 = global_timer_ns();
+            else if ((i & 127u) == 0 && global_timer_ns() - t0 > wc.limit_ns) break;
+            if (i > 4096) __nanosleep(32);
+        }
     }
-    *abort_flag = 1;
-    atomicOr(&g_error_word, err_code);
+    *wc.abort_flag = 1;
+    atomicOr(wc.err_word, err_code);
     return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& wc, unsigned int err_code) {
+    if (mbar_try_wait(bar, parity)) return true;              // common case: already complete
+    return mbar_wait_slow(bar, parity, wc, err_code);
+}
+
+// Book-keeping of a TMA producer: which load barriers it has armed last, so that a producer that
+// stops early (a wait for a free buffer gave up) can wait for the loads it has in flight before
+// the CTA exits - a bulk copy must not land in shared memory that no longer belongs to the CTA.
+template <int N>
+struct LoadTracker {
+    uint64_t* bar[N];
+    uint32_t par[N];
+    uint32_t armed = 0;
+    bool ok = true;
+    // waits (bounded) until `empty` says the buffer is free; false once any wait has given up
+    __device__ __forceinline__ bool acquire(uint64_t* empty, uint32_t parity, const WaitCtx& wc) {
+        if (ok) ok = mbar_wait(empty, parity, wc, kErrLoadWait);
+        return ok;
+    }
+    __device__ __forceinline__ void arm(int slot, uint64_t* full, uint32_t parity, uint32_t bytes) {
+        bar[slot] = full;
+        par[slot] = parity;
+        armed |= 1u << slot;
+        mbar_expect_tx(full, bytes);
+    }
+    // only after a give-up: every armed barrier completes when its bytes have landed
+    __device__ __forceinline__ void drain(const WaitCtx& wc) {
+        if (ok) return;
+#pragma unroll
+        for (int s = 0; s < N; ++s)
+            if ((armed >> s) & 1u) mbar_wait(bar[s], par[s], wc, kErrLoadWait);
+    }
+};
 
 // Generic-proxy writes to shared memory become visible to the async proxy (TMA, UMMA).
 __device__ __forceinline__ void fence_proxy_async() {
@@ -97,24 +154,27 @@ __device__ __forceinline__ void fence_proxy_async() {
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
-// 4-D tiled load global -> shared, completion on an mbarrier of this CTA.  No multicast.
-// c0 is the innermost coordinate; c0 * element size must be a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, uint64_t* bar,
-                                            int c0, int c1, int c2, int c3) {
+// 5-D tiled load global -> shared, completion on an mbarrier of this CTA.  No multicast.
+// Coordinates are (channel, column, row, head, batch); the channel coordinate times the element
+// size must be a multiple of 16 bytes.  Loads may start outside the tensor (the box is filled
+// with zeros there).
+__device__ __forceinline__ void tma_load_5d(void* dst, const void* tmap, uint64_t* bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
     asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)),
-          "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+          "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
 
-// 4-D tiled store shared -> global (bulk async-group completion).  Pixels of the box that lie
+// 5-D tiled store shared -> global (bulk async-group completion).  Pixels of the box that lie
 // outside the tensor are not written.  Coordinates must not be negative; c0 as for loads.
-__device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t smem_src, int c0, int c1, int c2, int c3) {
+__device__ __forceinline__ void tma_store_5d(const void* tmap, uint32_t smem_src, int c0, int c1, int c2, int c3,
+                                             int c4) {
     asm volatile(
-        "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-        ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        "cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }

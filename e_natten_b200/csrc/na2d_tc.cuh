@@ -9,7 +9,11 @@
 // the 128-byte (64-byte for head dim 32) swizzle, which is at once the K-major B operand of
 // S = Q K^T and the MN-major B operand of O = P V.  The per-query window mask is applied in
 // registers on the S accumulator read back from tensor memory, followed by an online softmax
-// across chunks; P goes back to shared memory as the K-major A operand of the second MMA.
+// across chunks; P goes back into tensor memory as packed 16-bit pairs, where it is the A operand
+// of the second MMA (TS form).
+//
+// This header holds what the kernel files share.  Each kernel family is compiled in a translation
+// unit of its own (na2d_tc_fwd.cu, na2d_tc_dq.cu, na2d_tc_dkdv.cu), once per 16-bit type.
 #pragma once
 
 #include <cuda.h>
@@ -18,6 +22,8 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include <atomic>
+#include <cstring>
 #include <mutex>
 
 #include "../../include/na2d.h"
@@ -106,6 +112,50 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// Low and high 64 bits of the mask with bit r * hw set for r < rc (rc * hw <= 128).
+constexpr unsigned long long row_repeat_lo(int hw, int rc) {
+    unsigned long long m = 0;
+    for (int r = 0; r < rc; ++r) if (r * hw < 64) m |= 1ull << (r * hw);
+    return m;
+}
+constexpr unsigned long long row_repeat_hi(int hw, int rc) {
+    unsigned long long m = 0;
+    for (int r = 0; r < rc; ++r) if (r * hw >= 64) m |= 1ull << (r * hw - 64);
+    return m;
+}
+
+// 128-bit helpers on (lo, hi) pairs.
+__device__ __forceinline__ void shl128(unsigned long long& lo, unsigned long long& hi, int s) {   // 0 <= s < 64
+    if (s > 0) {
+        hi = (hi << s) | (lo >> (64 - s));
+        lo <<= s;
+    }
+}
+// Bits [0, k) set, 0 <= k <= 128.
+__device__ __forceinline__ void low_bits128(int k, unsigned long long& lo, unsigned long long& hi) {
+    lo = k >= 64 ? ~0ull : ((1ull << k) - 1ull);
+    hi = k >= 128 ? ~0ull : (k > 64 ? ((1ull << (k - 64)) - 1ull) : 0ull);
+}
+
+// Validity of the 16 chunk columns [16 * blk, 16 * blk + 16) for one query: bit e is set when column
+// 16 * blk + e is a key of the query's window.  A chunk holds RC box rows of HW keys each (column
+// j = r * HW + c); the window covers chunk rows [wr_rel, wr_rel + KS) (wr_rel may be negative or
+// beyond the chunk) and box columns [wc, wc + KS).  Sixteen columns touch at most three box rows.
+template <int HW, int KS, int RC>
+__device__ __forceinline__ uint32_t block_mask16(int blk, int wr_rel, int wc) {
+    static_assert(3 * HW <= 64 && HW >= 8, "three box rows must fit 64 bits");
+    const unsigned long long cm = static_cast<unsigned long long>(((1u << KS) - 1u) << wc);
+    const int j0 = 16 * blk;
+    const int r0 = j0 / HW, c0 = j0 - r0 * HW;
+    unsigned long long w = 0;
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+        const int r = r0 + t;
+        if (r >= wr_rel && r < wr_rel + KS && r < RC) w |= cm << (t * HW);
+    }
+    return static_cast<uint32_t>(w >> c0) & 0xffffu;
+}
+
 // Output rows leave through TMA: a thread that wrote its own 16-byte pieces straight to global
 // memory would touch 32 different 128-byte lines per warp instruction.  Each softmax warp owns a
 // staging buffer of 32 pixels (32 / TW tile rows x TW columns) x OUT_RW channels, laid out as the
@@ -119,10 +169,11 @@ template <int DH> struct OutStage {
 };
 
 // Stores columns [0, DH) held as fp32 bit patterns in `v` (scaled by `scale`) as 16-bit channels
-// [ch0, ch0 + DH) of the warp's 32 pixels, whose first tile row is image row h0 and first column w0.
+// [ch0, ch0 + DH) of the warp's 32 pixels, whose first tile row is image row h0 and first column w0,
+// of head n of batch b.
 template <typename DT, int DH>
 __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint8_t* stage, const uint32_t (&v)[DH],
-                                                float scale, int ch0, int w0, int h0, int bn, int lane) {
+                                                float scale, int ch0, int w0, int h0, int n, int b, int lane) {
     using S = OutStage<DH>;
     const uint32_t row = smem_u32(stage) + lane * S::ROWB;
     const int sw = S::ROWB == 64 ? ((lane >> 1) & 3) : ((lane >> 2) & 1);
@@ -140,7 +191,7 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint8_t*
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-            tma_store_4d(map, smem_u32(stage), ch0 + r * S::RW, w0, h0, bn);
+            tma_store_5d(map, smem_u32(stage), ch0 + r * S::RW, w0, h0, n, b);
             bulk_commit();
         }
     }
@@ -194,26 +245,89 @@ inline EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Tensor map over a dense (BN, rows, W, C) tensor of 16-bit elements; the box is
-// (min(C, 64) channels) x box_w x box_h x 1, swizzled so that one box row is one swizzle span.
-// box_c = 0 takes min(C, 64) channels; the output maps of the epilogue pass 16 or 32.
-inline int make_map(CUtensorMap* map, const void* base, int dtype, long long BN, int rows, int W, int C,
+// One operand of a launch: base pointer and element strides of a (B, N, rows, W, C) tensor.
+struct TensorArg {
+    const void* ptr;
+    Na2dStride st;
+};
+
+// Tensor map over a (B, N, rows, W, C) tensor of 16-bit elements with the caller's strides
+// (channels contiguous); coordinates are (channel, column, row, head, batch).  The box is
+// box_c channels (0: min(C, 64)) x box_w x box_h x 1 x 1, swizzled so that one box row is one
+// swizzle span.  Encoded maps are kept in a small per-thread cache: a training loop calls with the
+// same buffers step after step, and the driver call is a visible part of a small launch.
+inline int make_map(CUtensorMap* map, const TensorArg& t, int dtype, int B, int N, int rows, int W, int C,
                     int box_w, int box_h, int box_c = 0) {
+    struct Key {
+        const void* ptr;
+        long long sb, sn, sh, sw;
+        int dtype, B, N, rows, W, C, box_w, box_h, box_c, pad;
+    };
+    struct Entry {
+        Key key;
+        CUtensorMap map;
+        bool used;
+    };
+    constexpr int kEntries = 64;
+    thread_local Entry cache[kEntries];
+    thread_local int next = 0;
+    Key key;
+    std::memset(&key, 0, sizeof(key));
+    key.ptr = t.ptr; key.sb = t.st.b; key.sn = t.st.n; key.sh = t.st.h; key.sw = t.st.w;
+    key.dtype = dtype; key.B = B; key.N = N; key.rows = rows; key.W = W; key.C = C;
+    key.box_w = box_w; key.box_h = box_h; key.box_c = box_c;
+    for (int i = 0; i < kEntries; ++i) {
+        if (cache[i].used && std::memcmp(&cache[i].key, &key, sizeof(Key)) == 0) {
+            *map = cache[i].map;
+            return NA2D_OK;
+        }
+    }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return NA2D_ERR_CUDA;
     const int slab_c = box_c > 0 ? box_c : (C < 64 ? C : 64);
-    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)rows, (cuuint64_t)BN};
-    cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)rows * W * C * 2};
-    cuuint32_t box[4] = {(cuuint32_t)slab_c, (cuuint32_t)box_w, (cuuint32_t)box_h, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
+    cuuint64_t dims[5] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)rows, (cuuint64_t)N, (cuuint64_t)B};
+    cuuint64_t strides[4] = {(cuuint64_t)t.st.w * 2, (cuuint64_t)t.st.h * 2, (cuuint64_t)t.st.n * 2,
+                             (cuuint64_t)t.st.b * 2};
+    cuuint32_t box[5] = {(cuuint32_t)slab_c, (cuuint32_t)box_w, (cuuint32_t)box_h, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     const CUtensorMapDataType dt = dtype == NA2D_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = slab_c * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                   : (slab_c * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
-    CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+    CUresult r = fn(map, dt, 5, const_cast<void*>(t.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) last_driver_result() = (int)r;
-    return r == CUDA_SUCCESS ? NA2D_OK : NA2D_ERR_CUDA;
+    if (r != CUDA_SUCCESS) {
+        last_driver_result() = (int)r;
+        return NA2D_ERR_CUDA;
+    }
+    cache[next].key = key;
+    cache[next].map = *map;
+    cache[next].used = true;
+    next = (next + 1) % kEntries;
+    return NA2D_OK;
 }
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device instead of on every
+// launch.  `done` is a per-kernel bit set (one bit per device ordinal).
+template <typename K>
+inline cudaError_t opt_in_smem(K kern, int bytes, int device, std::atomic<unsigned long long>& done) {
+    const unsigned long long bit = 1ull << (device & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+    return e;
+}
+
+// What every launcher gets besides the tensors: geometry, element type, device, stream, the device
+// error word of `device`, and a counter of launched kernels.
+struct LaunchCtx {
+    Na2dGeom g;
+    int dtype;
+    int B;
+    int device;
+    cudaStream_t st;
+    unsigned int* err_word;
+    int* launched;
+};
 
 // Register re-balancing of the 384-thread kernels (launched with 168 registers per thread): the
 // four warps of the data-movement group shrink to kRegsDonor, the eight softmax warps grow to
@@ -272,8 +386,8 @@ inline bool supported(int dtype, int C, int ks) {
 #ifdef NA2D_TRACE
 // Development aid (not compiled into the shipped library): CTA 0 records the SM clock at the
 // hand-overs between the warps so that they can be laid out on a time line.
-__device__ unsigned long long g_trace[8192];     // [role 0..3][unit 0..255][event 0..7]
-__device__ unsigned int g_trace_n = 8192;
+static __device__ unsigned long long g_trace[8192];     // [role 0..3][unit 0..255][event 0..7]
+static __device__ unsigned int g_trace_n = 8192;
 __device__ __forceinline__ void trace(int role, int ev, unsigned n) {
     if (blockIdx.x != 0 || n >= 256) return;
     g_trace[(role * 256 + n) * 8 + ev] = clock64();
@@ -282,28 +396,5 @@ __device__ __forceinline__ void trace(int role, int ev, unsigned n) {
 #else
 #define NA2D_TR(role, ev, n)
 #endif
-
-}  // namespace na2d_tc
-
-#include "na2d_tc_dq1.cuh"
-#include "na2d_tc_fwd1.cuh"
-#include "na2d_tc_fwd.cuh"
-#include "na2d_tc_bwd.cuh"
-#include "na2d_tc_dkdv.cuh"
-
-namespace na2d_tc {
-
-inline int read_and_clear_error(unsigned int* word, cudaStream_t st) {
-    if (cudaMemcpyFromSymbolAsync(word, g_error_word, sizeof(unsigned int), 0, cudaMemcpyDeviceToHost, st) != cudaSuccess)
-        return NA2D_ERR_CUDA;
-    if (cudaStreamSynchronize(st) != cudaSuccess) return NA2D_ERR_CUDA;
-    if (*word != 0) {
-        unsigned int zero = 0;
-        if (cudaMemcpyToSymbolAsync(g_error_word, &zero, sizeof(unsigned int), 0, cudaMemcpyHostToDevice, st) != cudaSuccess)
-            return NA2D_ERR_CUDA;
-        if (cudaStreamSynchronize(st) != cudaSuccess) return NA2D_ERR_CUDA;
-    }
-    return NA2D_OK;
-}
 
 }  // namespace na2d_tc

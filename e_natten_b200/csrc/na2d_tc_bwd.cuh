@@ -1,39 +1,57 @@
 // Persistent, warp-specialised tcgen05 dQ kernel (also produces the row delta).  Included by
-// na2d_tc.cuh.
+// na2d_tc_dq.cu.
 //
 // One CTA per SM walks query tiles (TH x TW queries, row r of every MMA = query r =
 // tensor-memory lane r).  The tile's halo box of keys is taken in chunks of whole box rows.
 //     S = Q K_c^T,  dP = dO V_c^T                          (tensor memory, fp32)
 //     p = exp(S - lse),  delta = sum_j p dP                (softmax warps, registers)
-//     dS = p (dP - delta)  -> tensor memory, 16 bit        (head + residual on the bf16 path)
+//     dS = scale p (dP - delta)  -> tensor memory, 16 bit  (head + residual on the bf16 path)
 //     dQ += dS K_c                                         (dS read from tensor memory)
-// delta needs every chunk of the tile before any dS can be formed.  With one chunk (kernel sizes
-// up to 5: at most 256 keys) a tile is a single unit and dQ reuses the S columns.  With several
-// chunks (at most 192 keys each) the tile is walked twice: units 0..NCH-1 only add up delta,
-// units NCH..2NCH-1 repeat the two score MMAs and accumulate dQ.
+// delta needs every chunk of the tile before any dS can be formed exactly.  With one chunk (kernel
+// sizes up to 5: at most 256 keys) a tile is a single unit and dQ reuses the S columns.  With
+// several chunks there are two ways:
+//   * one walk with a correction.  The caller hands in an estimate d~ of delta (dO . o from the
+//     stored output, see na2d_delta.cuh; off by the rounding of o, a few 1e-2 at most).  Every
+//     unit forms dS~ = scale p (dP - d~), adds dS~ K_c to dQ and, with one more MMA, p K_c to a
+//     second accumulator B, while the exact delta = sum_j p dP builds up in registers.  Since
+//     sum_j p (dP - delta) k = sum_j p (dP - d~) k - (delta - d~) sum_j p k, the epilogue stores
+//     dQ - scale (delta - d~) B.  B only meets the small factor (delta - d~), so a single 16-bit
+//     p is enough for it.  The exact delta is what the kernel writes out for the dK/dV kernel.
+//   * two walks (no estimate given): units 0..NCH-1 only add up delta, units NCH..2NCH-1 repeat
+//     the two score MMAs and accumulate dQ.
 // Twelve warps: 0-7 softmax (warps w and w+4 share 32 queries and split the 16-column blocks),
 // 8 TMA producer, 9 MMA issue, 10-11 idle (register donors).
 #pragma once
 
 namespace na2d_tc {
 
+// Keys per chunk at most: the whole box where it fits 256 columns (a single unit); else what
+// leaves room in tensor memory for S, dP and the two output accumulators dQ and B.
+constexpr int dq_nmax(int d, int ks) {
+    return (TH + ks - 1) * (TW + ks - 1) <= 256 ? 256 : (d == 128 ? 128 : 192);
+}
+
 template <int D, int KS, bool SPLIT>
-struct DqCfg : Cfg<D, KS, ((TH + KS - 1) * (TW + KS - 1) <= 256 ? 256 : 192)> {
-    using B = Cfg<D, KS, ((TH + KS - 1) * (TW + KS - 1) <= 256 ? 256 : 192)>;
+struct DqCfg : Cfg<D, KS, dq_nmax(D, KS)> {
+    using B = Cfg<D, KS, dq_nmax(D, KS)>;
     static constexpr bool ONE = B::NCH == 1;
-    static constexpr int UNITS = ONE ? 1 : 2 * B::NCH;                 // units per tile
+    static constexpr int NMAX = dq_nmax(D, KS);
     static constexpr int TMEM_S = 0;
-    static constexpr int TMEM_DP = ONE ? 256 : 192;
-    static constexpr int TMEM_DQ = ONE ? 0 : 384;                      // one chunk: dQ reuses the S columns
+    static constexpr int TMEM_DP = NMAX;
+    static constexpr int TMEM_DQ = ONE ? 0 : 2 * NMAX;                 // one chunk: dQ reuses the S columns
+    static constexpr int TMEM_BK = ONE ? 0 : 2 * NMAX + D;             // sum_j p k (several chunks only)
     static constexpr int TMEM_DSH = TMEM_DP;                           // dS (head) over dP
-    static constexpr int TMEM_RES = ONE ? 384 : 0;                     // dS residual: upper dP half / over S
+    static constexpr int TMEM_RES = ONE ? 384 : 0;                     // dS residual: upper dP half / lower half of S
+    static constexpr int TMEM_PH = B::NKP / 2;                         // p (head): upper half of S (several chunks only)
     static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;       // output staging of the 8 softmax warps
     static constexpr int FIXED = 2 * B::Q_BYTES + OUT_BYTES + 2 * 2 * 128 * 4 /*delta exchange*/ + 256 + 1024;
     static constexpr int SMEM = FIXED + 2 * B::KV_BYTES;               // one K chunk, one V chunk
     static constexpr int NB16 = (B::NKP + 15) / 16;
     static_assert(SMEM <= kSmemLimit, "dQ kernel shared memory");
-    static_assert(ONE ? (B::NKP <= 256) : (B::NKP <= 192), "tensor memory layout");
-    static_assert(!SPLIT || B::NKP / 2 <= (ONE ? 128 : 192), "residual operand does not fit");
+    static_assert(B::NKP <= NMAX, "tensor memory layout");
+    static_assert(ONE || TMEM_BK + D <= 512, "tensor memory layout");
+    static_assert(!SPLIT || !ONE || B::NKP / 2 <= 128, "residual operand does not fit");
+    static_assert((B::NKP / 2) % 8 == 0, "operand halves start on a block boundary");
 };
 
 template <typename DT, int D, int KS>
@@ -41,11 +59,11 @@ __global__ void __launch_bounds__(384, 1)
 dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
           const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
           const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse, float* __restrict__ delta,
-          const int want_dq_arg,
+          const float* __restrict__ delta_in, const int want_dq_arg, unsigned int* __restrict__ err_word,
           const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
     constexpr bool SPLIT = IsBf16<DT>::value;
     using C = DqCfg<D, KS, SPLIT>;
-    constexpr int NCH = C::NCH, UNITS = C::UNITS;
+    constexpr int NCH = C::NCH;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
@@ -68,6 +86,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     uint64_t* dq_free = bars + 10;           // softmax -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -112,49 +131,57 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    auto decode = [&](int i, int& bn, int& r0, int& c0) {
+    // my i-th tile: unit bn = head hn of batch hb, first row r0, first column c0
+    auto decode = [&](int i, int& bn, int& hn, int& hb, int& r0, int& c0) {
         int t = (int)blockIdx.x + i * (int)gridDim.x;
         const int tc = t % tiles_c;
         t /= tiles_c;
         r0 = (t % tiles_r) * TH;
         c0 = tc * TW;
         bn = t / tiles_r;
+        hb = bn / g.N;
+        hn = bn - hb * g.N;
     };
-    // A unit u of a tile works on chunk u % NCH; units >= NCH (or the only unit) form dS and dQ.
+    // A unit u of a tile works on chunk u % NCH.  Units from first_ds on form dS and add to dQ; the
+    // units before it (a first walk, only when no estimate of delta is given) add up delta.
     // Without a dQ output only the delta units run.
-    const int units_run = want_dq ? UNITS : (C::ONE ? 1 : NCH);
+    const bool given = !C::ONE && want_dq && delta_in != nullptr;      // one walk with the correction
+    const int first_ds = (C::ONE || given) ? 0 : NCH;
+    const int units_run = want_dq ? first_ds + NCH : NCH;
 
     if (warp == 8) {
         // ------------------------------------------------------------------ producer
         reg_dec<kRegsDonor>();
         if (lane == 0) {
             uint32_t n = 0;
-            for (int i = 0; i < n_my; ++i) {
-                int bn, r0, c0;
-                decode(i, bn, r0, c0);
+            LoadTracker<3> lt;                                   // slots: Q / dO tile, V chunk, K chunk
+            for (int i = 0; i < n_my && lt.ok; ++i) {
+                int bn, hn, hb, r0, c0;
+                decode(i, bn, hn, hb, r0, c0);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
-                mbar_wait(q_empty, (i & 1) ^ 1, abort_flag, kErrLoadWait);
-                mbar_expect_tx(q_full, 2u * C::Q_BYTES);
+                if (!lt.acquire(q_empty, (i & 1) ^ 1, wctx)) break;
+                lt.arm(0, q_full, i & 1, 2u * C::Q_BYTES);
 #pragma unroll
                 for (int s = 0; s < C::NS; ++s) {
-                    tma_load_4d(sQ + s * C::Q_SLAB, &tm_q, q_full, s * 64, c0, r0, bn);
-                    tma_load_4d(sDO + s * C::Q_SLAB, &tm_do, q_full, s * 64, c0, r0, bn);
+                    tma_load_5d(sQ + s * C::Q_SLAB, &tm_q, q_full, s * 64, c0, r0, hn, hb);
+                    tma_load_5d(sDO + s * C::Q_SLAB, &tm_do, q_full, s * 64, c0, r0, hn, hb);
                 }
                 for (int u = 0; u < units_run; ++u, ++n) {
                     const int c = u % NCH;
-                    mbar_wait(v_empty, (n & 1) ^ 1, abort_flag, kErrLoadWait);
-                    mbar_expect_tx(v_full, (uint32_t)C::NS * C::NK * C::ROWB);
+                    if (!lt.acquire(v_empty, (n & 1) ^ 1, wctx)) break;
+                    lt.arm(1, v_full, n & 1, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
-                        tma_load_4d(sV + s * C::KV_SLAB, &tm_v, v_full, s * 64, box_c0, box_r0 + c * C::RC, bn);
-                    mbar_wait(k_empty, (n & 1) ^ 1, abort_flag, kErrLoadWait);
-                    mbar_expect_tx(k_full, (uint32_t)C::NS * C::NK * C::ROWB);
+                        tma_load_5d(sV + s * C::KV_SLAB, &tm_v, v_full, s * 64, box_c0, box_r0 + c * C::RC, hn, hb);
+                    if (!lt.acquire(k_empty, (n & 1) ^ 1, wctx)) break;
+                    lt.arm(2, k_full, n & 1, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
-                        tma_load_4d(sK + s * C::KV_SLAB, &tm_k, k_full, s * 64, box_c0, box_r0 + c * C::RC, bn);
+                        tma_load_5d(sK + s * C::KV_SLAB, &tm_k, k_full, s * 64, box_c0, box_r0 + c * C::RC, hn, hb);
                 }
             }
+            lt.drain(wctx);
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
@@ -168,22 +195,22 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
         const uint32_t km_lo = smem_desc_lo(smem_u32(sK), C::KV_SLAB);
         uint32_t n = 0, n_free = 0, n_p = 0;          // units, delta-only units, dS units so far
         for (int i = 0; i < n_my; ++i) {
-            mbar_wait(q_full, i & 1, abort_flag, kErrLoadWait);
+            mbar_wait(q_full, i & 1, wctx, kErrLoadWait);
             for (int u = 0; u < units_run; ++u, ++n) {
-                const bool forms_ds = want_dq && (C::ONE || u >= NCH);
+                const bool forms_ds = want_dq && u >= first_ds;
                 if (leader) NA2D_TR(2, 0, n);
-                mbar_wait(k_full, n & 1, abort_flag, kErrLoadWait);
-                mbar_wait(v_full, n & 1, abort_flag, kErrLoadWait);
+                mbar_wait(k_full, n & 1, wctx, kErrLoadWait);
+                mbar_wait(v_full, n & 1, wctx, kErrLoadWait);
                 // the accumulators the score MMAs overwrite must have been read
-                if (u > 0 && !(C::ONE) && u <= NCH) {            // previous unit was delta-only
-                    mbar_wait(s_free, (n_free & 1) ^ 1, abort_flag, kErrMmaWait);
+                if (u > 0 && !(want_dq && u - 1 >= first_ds)) {  // previous unit was delta-only
+                    mbar_wait(s_free, (n_free & 1) ^ 1, wctx, kErrMmaWait);
                 }
                 if (u == 0 && i > 0) {
                     if (C::ONE || !want_dq) {
                         // previous tile: its last unit either left dQ over S (epilogue must have read
                         // it) or was delta-only (S must have been read)
-                        if (want_dq) mbar_wait(dq_free, (i & 1) ^ 1, abort_flag, kErrMmaWait);
-                        else mbar_wait(s_free, (n_free & 1) ^ 1, abort_flag, kErrMmaWait);
+                        if (want_dq) mbar_wait(dq_free, (i & 1) ^ 1, wctx, kErrMmaWait);
+                        else mbar_wait(s_free, (n_free & 1) ^ 1, wctx, kErrMmaWait);
                     }
                 }
                 tc_fence_after();
@@ -211,13 +238,13 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 }
                 __syncwarp();
                 if (!forms_ds) { ++n_free; continue; }
-                mbar_wait(p_full, n_p & 1, abort_flag, kErrMmaWait);
+                mbar_wait(p_full, n_p & 1, wctx, kErrMmaWait);
                 ++n_p;
-                if (!C::ONE && u == NCH && i > 0) mbar_wait(dq_free, (i & 1) ^ 1, abort_flag, kErrMmaWait);
+                if (!C::ONE && u == first_ds && i > 0) mbar_wait(dq_free, (i & 1) ^ 1, wctx, kErrMmaWait);
                 tc_fence_after();
                 if (elect_one()) {
                     NA2D_TR(2, 3, n);
-                    const uint32_t acc = (!C::ONE && u > NCH) ? 1u : 0u;
+                    const uint32_t acc = (!C::ONE && u > first_ds) ? 1u : 0u;
 #pragma unroll
                     for (int kk = 0; kk < C::NKP / 16; ++kk)
                         umma_ts(tmem_base + C::TMEM_DQ, tmem_base + C::TMEM_DSH + 8 * kk,
@@ -227,6 +254,12 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                         for (int kk = 0; kk < C::NKP / 16; ++kk)
                             umma_ts(tmem_base + C::TMEM_DQ, tmem_base + C::TMEM_RES + 8 * kk,
                                     desc64(hi, km_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, 1u);
+                    }
+                    if (given) {                                 // B (+)= p K_c
+#pragma unroll
+                        for (int kk = 0; kk < C::NKP / 16; ++kk)
+                            umma_ts(tmem_base + C::TMEM_BK, tmem_base + C::TMEM_PH + 8 * kk,
+                                    desc64(hi, km_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
                     }
                     umma_commit(k_empty);
                     if (u == units_run - 1) umma_commit(dq_full);
@@ -251,8 +284,8 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 
         uint32_t n = 0, n_x = 0;                             // units, delta exchanges so far
         for (int i = 0; i < n_my; ++i) {
-            int bn, r0, c0;
-            decode(i, bn, r0, c0);
+            int bn, hn, hb, r0, c0;
+            decode(i, bn, hn, hb, r0, c0);
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
             const int qr_raw = r0 + (row / TW), qc_raw = c0 + (row % TW);
@@ -264,12 +297,17 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
             const int wr_lo = __shfl_sync(0xffffffffu, wr, 0);
             const int wr_hi = __shfl_sync(0xffffffffu, wr, 31);
             const float lse2 = lse[qi] * kLog2e;
-            float dl_part = 0.f, dl = 0.f;                   // this half's part of delta; delta
+            float dl_part = 0.f;                             // this half's part of delta
+            float dl = 0.f;                                  // delta, once every chunk has been seen
+            // The estimate is read before this tile's first partner barrier and the exact value
+            // written (by the partner warp of half 0, to the same address when delta_in == delta)
+            // after its last one, so the read never sees the new value.
+            const float d_est = given ? delta_in[qi] : 0.f;
 
             for (int u = 0; u < units_run; ++u, ++n) {
                 const int ch = u % NCH;
-                const bool forms_ds = want_dq && (C::ONE || u >= NCH);
-                const bool adds_delta = C::ONE || u < NCH;
+                const bool forms_ds = want_dq && u >= first_ds;
+                const bool adds_delta = C::ONE || given || u < NCH;
                 const int row_off = ch * C::RC;
                 const int j_lo = max(wr_lo - row_off, 0) * C::HW;
                 const int j_hi = min(min(wr_hi + KS - row_off, C::RC) * C::HW, C::NK);       // exclusive
@@ -277,7 +315,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 const int bi_lo = ((j_lo >> 4) - half + 1) >> 1;
 
                 if (tid == 0) NA2D_TR(3, 0, n);
-                mbar_wait(s_full, n & 1, abort_flag, kErrMmaWait);
+                mbar_wait(s_full, n & 1, wctx, kErrMmaWait);
                 tc_fence_after();
                 if (tid == 0) NA2D_TR(3, 1, n);
                 uint32_t s[NACT][16], dp[NACT][16];
@@ -293,16 +331,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 #pragma unroll
                 for (int a = 0; a < NACT; ++a) {                             // validity masks, loads in flight
                     const int blk = half + 2 * (bi_lo + a);
-                    uint32_t m = 0;
-#pragma unroll
-                    for (int w = 0; w < KS; ++w) {
-                        const int r = wr + w - row_off;                       // chunk row of window row w
-                        const int rel = r * C::HW + wc - 16 * blk;            // its first column, relative to the block
-                        const uint32_t seg = (1u << KS) - 1u;
-                        const uint32_t bits = rel >= 0 ? (seg << (rel & 31)) : (seg >> ((-rel) & 31));
-                        if (r >= 0 && r < C::RC && rel > -KS && rel < 16) m |= bits;
-                    }
-                    vmask[a] = (blk < b_hi) ? (m & 0xffffu) : 0u;
+                    vmask[a] = (blk < b_hi) ? block_mask16<C::HW, KS, C::RC>(blk, wr - row_off, wc) : 0u;
                 }
                 tmem_ld_wait();
                 if (tid == 0) NA2D_TR(3, 2, n);
@@ -315,9 +344,9 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 #pragma unroll
                         for (int e = 0; e < 16; e += 2) {
                             const float p0 = ((vmask[a] >> e) & 1u)
-                                                 ? fast_exp2(fmaf(__uint_as_float(s[a][e]), kLog2e, -lse2)) : 0.f;
+                                                 ? fast_exp2(fmaf(__uint_as_float(s[a][e]), g.sl2, -lse2)) : 0.f;
                             const float p1 = ((vmask[a] >> (e + 1)) & 1u)
-                                                 ? fast_exp2(fmaf(__uint_as_float(s[a][e + 1]), kLog2e, -lse2)) : 0.f;
+                                                 ? fast_exp2(fmaf(__uint_as_float(s[a][e + 1]), g.sl2, -lse2)) : 0.f;
                             s[a][e] = __float_as_uint(p0);
                             s[a][e + 1] = __float_as_uint(p1);
                             // masked columns may hold anything (padding keys): keep them out by
@@ -351,7 +380,9 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                     continue;
                 }
 
-                // dS = p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path)
+                // dS = scale * p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path);
+                // with the one-walk scheme delta is the estimate, and p goes along as a third operand
+                const float dls = (given ? d_est : dl) * g.scale;
 #pragma unroll
                 for (int a = 0; a < NACT; ++a) {
                     const int blk = half + 2 * (bi_lo + a);
@@ -360,14 +391,20 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 #pragma unroll
                         for (int e2 = 0; e2 < 8; ++e2) {
                             const float ds0 = ((vmask[a] >> (2 * e2)) & 1u)
-                                ? __uint_as_float(s[a][2 * e2]) * (__uint_as_float(dp[a][2 * e2]) - dl) : 0.f;
+                                ? __uint_as_float(s[a][2 * e2]) * fmaf(__uint_as_float(dp[a][2 * e2]), g.scale, -dls) : 0.f;
                             const float ds1 = ((vmask[a] >> (2 * e2 + 1)) & 1u)
-                                ? __uint_as_float(s[a][2 * e2 + 1]) * (__uint_as_float(dp[a][2 * e2 + 1]) - dl) : 0.f;
+                                ? __uint_as_float(s[a][2 * e2 + 1]) * fmaf(__uint_as_float(dp[a][2 * e2 + 1]), g.scale, -dls) : 0.f;
                             wd[e2] = pack2<DT>(ds0, ds1);
                             wr2[e2] = SPLIT ? pack2_residual_bf16(ds0, ds1, wd[e2]) : 0u;
                         }
                         tmem_st_32x8(tmem_lane + C::TMEM_DSH + 8 * blk, wd);
                         if (SPLIT) tmem_st_32x8(tmem_lane + C::TMEM_RES + 8 * blk, wr2);
+                        if (given) {                             // p of masked columns is an exact zero
+#pragma unroll
+                            for (int e2 = 0; e2 < 8; ++e2)
+                                wd[e2] = pack2<DT>(__uint_as_float(s[a][2 * e2]), __uint_as_float(s[a][2 * e2 + 1]));
+                            tmem_st_32x8(tmem_lane + C::TMEM_PH + 8 * blk, wd);
+                        }
                     }
                 }
                 {   // own blocks outside the range hold zeros
@@ -378,6 +415,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                         if (!in_range && 16 * blk < C::NKP) {
                             tmem_st_32x8(tmem_lane + C::TMEM_DSH + 8 * blk, z);
                             if (SPLIT) tmem_st_32x8(tmem_lane + C::TMEM_RES + 8 * blk, z);
+                            if (given) tmem_st_32x8(tmem_lane + C::TMEM_PH + 8 * blk, z);
                         }
                     }
                 }
@@ -390,7 +428,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 
             if (want_dq) {
                 // ---- epilogue: this half's columns of the thread's dQ row
-                mbar_wait(dq_full, i & 1, abort_flag, kErrMmaWait);
+                mbar_wait(dq_full, i & 1, wctx, kErrMmaWait);
                 tc_fence_after();
                 if (tid == 0) NA2D_TR(3, 5, n - 1);
                 uint32_t acc[DH];
@@ -398,13 +436,26 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 for (int piece = 0; piece < DH / 16; ++piece)
                     tmem_ld_32x16(tmem_lane + C::TMEM_DQ + half * DH + 16 * piece,
                                   *reinterpret_cast<uint32_t(*)[16]>(&acc[16 * piece]));
+                if (given) {
+                    // dQ - scale (delta - estimate) B, piece by piece
+                    const float corr = (dl - d_est) * g.scale;
+#pragma unroll
+                    for (int piece = 0; piece < DH / 16; ++piece) {
+                        uint32_t bk[16];
+                        tmem_ld_32x16(tmem_lane + C::TMEM_BK + half * DH + 16 * piece, bk);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 16; ++e)
+                            acc[16 * piece + e] = __float_as_uint(fmaf(-corr, __uint_as_float(bk[e]), __uint_as_float(acc[16 * piece + e])));
+                    }
+                }
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dq_free);
                 if (tid == 0) NA2D_TR(3, 6, n - 1);
                 stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0,
-                                        r0 + quarter * (32 / TW), bn, lane);
+                                        r0 + quarter * (32 / TW), hn, hb, lane);
                 if (tid == 0) NA2D_TR(3, 7, n - 1);
             }
         }
@@ -419,43 +470,36 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     }
 }
 
+// delta_in: row deltas formed beforehand (or null: the kernel forms them itself and writes `delta`).
 template <typename DT, int D, int KS>
-int launch_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-              const void* d_o, void* d_q, float* delta, int device, cudaStream_t st, int* launched) {
+int launch_dq(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, const TensorArg& v, const float* lse,
+              const TensorArg& d_o, const TensorArg& d_q, float* delta, const float* delta_in) {
     // kernel sizes 3 and 5 with a dQ output go to the strip kernel; this one keeps the larger
     // windows and the delta-only call
     if constexpr (KS <= 5) {
-        if (d_q != nullptr) return launch_dq1<DT, D, KS>(g, dtype, q, k, v, lse, d_o, d_q, delta, device, st, launched);
+        if (d_q.ptr != nullptr) return launch_dq1<DT, D, KS>(lc, q, k, v, lse, d_o, d_q, delta);
     }
     using C = DqCfg<D, KS, IsBf16<DT>::value>;
+    const Na2dGeom& g = lc.g;
     CUtensorMap tq, tg, tk, tv, tdq;
-    int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
+    int rc = make_map(&tq, q, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, TH);
     // without a dQ buffer the kernel only writes delta; the map then points at q and is never used
-    if (rc == NA2D_OK) rc = make_map(&tdq, d_q ? d_q : q, dtype, g.BN, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
-    if (rc == NA2D_OK) rc = make_map(&tg, d_o, dtype, g.BN, g.Hq, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
-    if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
+    if (rc == NA2D_OK) rc = make_map(&tdq, d_q.ptr ? d_q : q, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
+    if (rc == NA2D_OK) rc = make_map(&tg, d_o, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&tk, k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, C::HW, C::RC);
+    if (rc == NA2D_OK) rc = make_map(&tv, v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc != NA2D_OK) return rc;
     const int tiles_r = (g.Hq + TH - 1) / TH, tiles_c = (g.W + TW - 1) / TW;
     const long long tiles = (long long)g.BN * tiles_r * tiles_c;
     if (tiles > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
     auto kern = dq_kernel<DT, D, KS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-        return NA2D_ERR_CUDA;
-    const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 384, C::SMEM, st>>>(tq, tg, tk, tv, tdq, lse, delta, d_q != nullptr, g, tiles_r, tiles_c, (int)tiles);
-    *launched += 1;
+    static std::atomic<unsigned long long> opted{0};
+    if (opt_in_smem(kern, C::SMEM, lc.device, opted) != cudaSuccess) return NA2D_ERR_CUDA;
+    const int grid = (int)(tiles < sm_count(lc.device) ? tiles : sm_count(lc.device));
+    kern<<<grid, 384, C::SMEM, lc.st>>>(tq, tg, tk, tv, tdq, lse, delta, delta_in, d_q.ptr != nullptr, lc.err_word, g,
+                                        tiles_r, tiles_c, (int)tiles);
+    *lc.launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
-}
-
-inline int backward_dq(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const void* /*o*/,
-                       const float* lse, const void* d_o, void* d_q, float* delta, int device, cudaStream_t st,
-                       int* launched) {
-    if (dtype == NA2D_BF16) {
-        NA2D_TC_DISPATCH_D(launch_dq, __nv_bfloat16, g, dtype, q, k, v, lse, d_o, d_q, delta, device, st, launched)
-    } else {
-        NA2D_TC_DISPATCH_D(launch_dq, __half, g, dtype, q, k, v, lse, d_o, d_q, delta, device, st, launched)
-    }
 }
 
 }  // namespace na2d_tc

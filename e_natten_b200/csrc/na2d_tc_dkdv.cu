@@ -1,0 +1,25 @@
+// Translation unit of the tcgen05 dK/dV kernels for one 16-bit element type
+// (-DNA2D_TC_DT=1: bf16, 2: fp16).
+#include "na2d_tc_entry.h"
+#include "na2d_tc_dkdv.cuh"
+
+namespace na2d_tc {
+
+#if NA2D_TC_DT == 1
+#define NA2D_TC_TYPE __nv_bfloat16
+#define NA2D_TC_NAME(base) base##_bf16
+#elif NA2D_TC_DT == 2
+#define NA2D_TC_TYPE __half
+#define NA2D_TC_NAME(base) base##_f16
+#else
+#error "compile with -DNA2D_TC_DT=1 (bf16) or 2 (fp16)"
+#endif
+
+int NA2D_TC_NAME(backward_dkdv)(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, const TensorArg& v,
+                                const float* lse, const TensorArg& d_o, const float* delta, const TensorArg& d_k,
+                                const TensorArg& d_v) {
+    const Na2dGeom& g = lc.g;
+    NA2D_TC_DISPATCH_D(launch_dkdv, NA2D_TC_TYPE, lc, q, k, v, lse, d_o, delta, d_k, d_v)
+}
+
+}  // namespace na2d_tc

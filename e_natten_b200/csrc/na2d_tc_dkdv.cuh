@@ -66,7 +66,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
             const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
             const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
             const float* __restrict__ lse, const float* __restrict__ delta,
-            DT* __restrict__ d_k, DT* __restrict__ d_v, const Na2dGeom g, const int tiles_r, const int tiles_c,
+            unsigned int* __restrict__ err_word, const Na2dGeom g, const int tiles_r, const int tiles_c,
             const int total_tiles) {
     constexpr bool SPLIT = IsBf16<DT>::value;
     using C = DkvCfg<D, KS, SPLIT>;
@@ -90,6 +90,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     uint64_t* st_free = bars + 16;           // [2]   output MMAs (commit) -> score MMAs: the stage is free
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -140,7 +141,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     const uint32_t tmem_base = *tmem_slot;
 
     // Geometry of my i-th tile: key tile origin and the query box it is seen from.
-    struct TileGeo { int bn, kr0, kc0, qb_r0, q_local_r0, n_rows, qb_c0, n_cc, n_ch; };
+    struct TileGeo { int bn, hn, hb, kr0, kc0, qb_r0, q_local_r0, n_rows, qb_c0, n_cc, n_ch; };
     auto tile_geo = [&](int i) {
         TileGeo t;
         int x = (int)blockIdx.x + i * (int)gridDim.x;
@@ -149,6 +150,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         t.kr0 = (x % tiles_r) * TH;
         t.kc0 = tc * TW;
         t.bn = x / tiles_r;
+        t.hb = t.bn / g.N;
+        t.hn = t.bn - t.hb * g.N;
         const int kg_first = g.kv_row0 + t.kr0;
         const int kg_last = g.kv_row0 + min(t.kr0 + TH, g.Hkv) - 1;
         t.qb_r0 = max(na2d_bws(kg_first, KS), g.q_row0);                           // global row
@@ -169,24 +172,26 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
             uint32_t n = 0;
-            for (int i = 0; i < n_my; ++i) {
+            LoadTracker<4> lt;                                   // slots: the ring's stages
+            for (int i = 0; i < n_my && lt.ok; ++i) {
                 const TileGeo t = tile_geo(i);
                 for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
                     const int rc = ch / t.n_cc, cc = ch - rc * t.n_cc;
                     const uint32_t st = n % NSTQ;
-                    mbar_wait(qd_empty + st, ((n / NSTQ) & 1) ^ 1, abort_flag, kErrLoadWait);
+                    if (!lt.acquire(qd_empty + st, ((n / NSTQ) & 1) ^ 1, wctx)) break;
                     NA2D_TR(2, 7, n);
-                    mbar_expect_tx(qd_full + st, 2u * C::NS * C::NK * C::ROWB);
+                    lt.arm(st, qd_full + st, (n / NSTQ) & 1, 2u * C::NS * C::NK * C::ROWB);
                     uint8_t* dst = sQD + st * C::STAGE;
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s) {
-                        tma_load_4d(dst + s * C::KV_SLAB, &tm_q, qd_full + st, s * 64, t.qb_c0 + cc * C::HW,
-                                    t.q_local_r0 + rc * C::RC, t.bn);
-                        tma_load_4d(dst + C::KV_BYTES + s * C::KV_SLAB, &tm_do, qd_full + st, s * 64,
-                                    t.qb_c0 + cc * C::HW, t.q_local_r0 + rc * C::RC, t.bn);
+                        tma_load_5d(dst + s * C::KV_SLAB, &tm_q, qd_full + st, s * 64, t.qb_c0 + cc * C::HW,
+                                    t.q_local_r0 + rc * C::RC, t.hn, t.hb);
+                        tma_load_5d(dst + C::KV_BYTES + s * C::KV_SLAB, &tm_do, qd_full + st, s * 64,
+                                    t.qb_c0 + cc * C::HW, t.q_local_r0 + rc * C::RC, t.hn, t.hb);
                     }
                 }
             }
+            lt.drain(wctx);
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue: scores
@@ -208,11 +213,11 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 const uint32_t q_lo = smem_desc_lo(q_addr, 16), g_lo = smem_desc_lo(g_addr, 16);
                 const uint32_t tm = tmem_base + (n & 1) * C::TMEM_STAGE;
                 if (lane == 0) NA2D_TR(2, 0, n);
-                if (ch == 0) mbar_wait(kv_full, it & 1, abort_flag, kErrLoadWait);
+                if (ch == 0) mbar_wait(kv_full, it & 1, wctx, kErrLoadWait);
                 if (lane == 0) NA2D_TR(2, 1, n);
-                mbar_wait(qd_full + n % NSTQ, (n / NSTQ) & 1, abort_flag, kErrLoadWait);
+                mbar_wait(qd_full + n % NSTQ, (n / NSTQ) & 1, wctx, kErrLoadWait);
                 if (lane == 0) NA2D_TR(2, 3, n);
-                mbar_wait(st_free + (n & 1), ((n >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
+                mbar_wait(st_free + (n & 1), ((n >> 1) & 1) ^ 1, wctx, kErrMmaWait);
                 if (lane == 0) NA2D_TR(2, 5, n);
                 tc_fence_after();
                 if (elect_one()) {
@@ -252,8 +257,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 const uint32_t qm_lo = smem_desc_lo(q_addr, C::KV_SLAB), gm_lo = smem_desc_lo(g_addr, C::KV_SLAB);
                 const uint32_t tm = tmem_base + (n & 1) * C::TMEM_STAGE;
                 const uint32_t acc = ch == 0 ? 0u : 1u;
-                mbar_wait(p_full + (n & 1), (n >> 1) & 1, abort_flag, kErrMmaWait);
-                if (ch == 0) mbar_wait(acc_free, (it & 1) ^ 1, abort_flag, kErrMmaWait);
+                mbar_wait(p_full + (n & 1), (n >> 1) & 1, wctx, kErrMmaWait);
+                if (ch == 0) mbar_wait(acc_free, (it & 1) ^ 1, wctx, kErrMmaWait);
                 tc_fence_after();
                 if (elect_one()) {
 #pragma unroll
@@ -283,24 +288,25 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
             uint32_t it = 0;                            // non-empty tile counter
+            LoadTracker<1> lt;
             for (int i = 0; i < n_my; ++i) {
                 const TileGeo t = tile_geo(i);
                 if (t.n_ch == 0) continue;
-                mbar_wait(kv_empty, (it & 1) ^ 1, abort_flag, kErrLoadWait);
-                mbar_expect_tx(kv_full, 2u * C::Q_BYTES);
+                if (!lt.acquire(kv_empty, (it & 1) ^ 1, wctx)) break;
+                lt.arm(0, kv_full, it & 1, 2u * C::Q_BYTES);
 #pragma unroll
                 for (int s = 0; s < C::NS; ++s) {
-                    tma_load_4d(sK + s * C::Q_SLAB, &tm_k, kv_full, s * 64, t.kc0, t.kr0, t.bn);
-                    tma_load_4d(sV + s * C::Q_SLAB, &tm_v, kv_full, s * 64, t.kc0, t.kr0, t.bn);
+                    tma_load_5d(sK + s * C::Q_SLAB, &tm_k, kv_full, s * 64, t.kc0, t.kr0, t.hn, t.hb);
+                    tma_load_5d(sV + s * C::Q_SLAB, &tm_v, kv_full, s * 64, t.kc0, t.kr0, t.hn, t.hb);
                 }
                 ++it;
             }
+            lt.drain(wctx);
         }
     } else if (warp >= 12) {
         // ------------------------------------------------------------------ epilogue warps
         reg_dec<kDkvRegsEpi>();
         const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;                 // key of the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         uint8_t* stage = sOut + quarter * OutStage<32>::BYTES;
         constexpr int RPO = D / 32;                          // 32-channel rounds per output
@@ -308,19 +314,17 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         for (int i = 0; i < n_my; ++i) {
             const TileGeo t = tile_geo(i);
             if (t.n_ch == 0) {                               // no local query sees this tile: zeros
-                const int kr = t.kr0 + (row / TW), kc = t.kc0 + (row % TW);
-                if (kr < g.Hkv && kc < g.W) {
-                    const size_t ki = (static_cast<size_t>(t.bn) * g.Hkv + kr) * g.W + kc;
+                uint32_t z[32];
 #pragma unroll
-                    for (int c8 = 0; c8 < D / 8; ++c8) {
-                        *reinterpret_cast<uint4*>(d_v + ki * D + 8 * c8) = make_uint4(0u, 0u, 0u, 0u);
-                        *reinterpret_cast<uint4*>(d_k + ki * D + 8 * c8) = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                }
+                for (int e = 0; e < 32; ++e) z[e] = 0u;
+#pragma unroll
+                for (int j = 0; j < 2 * RPO; ++j)
+                    stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
+                                            t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane);
                 continue;
             }
             if (warp == 12 && lane == 0) NA2D_TR(0, 0, it);
-            mbar_wait(acc_full, it & 1, abort_flag, kErrMmaWait);
+            mbar_wait(acc_full, it & 1, wctx, kErrMmaWait);
             tc_fence_after();
             if (warp == 12 && lane == 0) NA2D_TR(0, 1, it);
             const int h0 = t.kr0 + quarter * (32 / TW);
@@ -340,7 +344,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     if (warp == 12 && lane == 0) NA2D_TR(0, 2, it);
                 }
                 stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 1.f, 32 * (j % RPO), t.kc0, h0,
-                                        t.bn, lane);
+                                        t.hn, t.hb, lane);
             }
             if (warp == 12 && lane == 0) NA2D_TR(0, 3, it);
             ++it;
@@ -388,7 +392,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     if (br < t.n_rows && qc < g.W) {
                         const size_t qi = (static_cast<size_t>(t.bn) * g.Hq + (t.q_local_r0 + br)) * g.W + qc;
                         l2 = lse[qi] * kLog2e;
-                        dl = delta[qi];
+                        dl = delta[qi] * g.scale;      // dS carries the softmax scale: dK = scale * sum_i p (dP - delta) q
                     }
                     x_lse[gtid] = l2;
                     x_delta[gtid] = dl;
@@ -406,7 +410,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 bar_sync(5 + group, 128);                                   // lse / delta are in place
                 if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 1, n);
 
-                mbar_wait(s_full + group, k & 1, abort_flag, kErrMmaWait);
+                mbar_wait(s_full + group, k & 1, wctx, kErrMmaWait);
                 tc_fence_after();
                 if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 2, n);
                 uint32_t s[NACT][8], dp[NACT][8];
@@ -455,10 +459,10 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
                                 const int e = 2 * e2 + h;
-                                const float pe = fast_exp2(fmaf(__uint_as_float(s[a][e]), kLog2e, -l2[e]));
+                                const float pe = fast_exp2(fmaf(__uint_as_float(s[a][e]), g.sl2, -l2[e]));
                                 const bool ok = (vmask[a] >> e) & 1u;      // select, never multiply by zero
                                 p[h] = ok ? pe : 0.f;
-                                ds[h] = ok ? pe * (__uint_as_float(dp[a][e]) - dl[e]) : 0.f;
+                                ds[h] = ok ? pe * fmaf(__uint_as_float(dp[a][e]), g.scale, -dl[e]) : 0.f;
                             }
                             wp[e2] = pack2<DT>(p[0], p[1]);
                             wd[e2] = pack2<DT>(ds[0], ds[1]);
@@ -498,38 +502,29 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
 }
 
 template <typename DT, int D, int KS>
-int launch_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-                const void* d_o, const float* delta, void* d_k, void* d_v, int device, cudaStream_t st, int* launched) {
+int launch_dkdv(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, const TensorArg& v, const float* lse,
+                const TensorArg& d_o, const float* delta, const TensorArg& d_k, const TensorArg& d_v) {
     using C = DkvCfg<D, KS, IsBf16<DT>::value>;
+    const Na2dGeom& g = lc.g;
     CUtensorMap tk, tv, tq, tg, tdk, tdv;
-    int rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tdk, d_k, dtype, g.BN, g.Hkv, g.W, D, TW, 32 / TW, 32);
-    if (rc == NA2D_OK) rc = make_map(&tdv, d_v, dtype, g.BN, g.Hkv, g.W, D, TW, 32 / TW, 32);
-    if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, C::HW, C::RC);
-    if (rc == NA2D_OK) rc = make_map(&tg, d_o, dtype, g.BN, g.Hq, g.W, D, C::HW, C::RC);
+    int rc = make_map(&tk, k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&tdk, d_k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, 32 / TW, 32);
+    if (rc == NA2D_OK) rc = make_map(&tdv, d_v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, 32 / TW, 32);
+    if (rc == NA2D_OK) rc = make_map(&tv, v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&tq, q, lc.dtype, lc.B, g.N, g.Hq, g.W, D, C::HW, C::RC);
+    if (rc == NA2D_OK) rc = make_map(&tg, d_o, lc.dtype, lc.B, g.N, g.Hq, g.W, D, C::HW, C::RC);
     if (rc != NA2D_OK) return rc;
     const int tiles_r = (g.Hkv + TH - 1) / TH, tiles_c = (g.W + TW - 1) / TW;
     const long long tiles = (long long)g.BN * tiles_r * tiles_c;
     if (tiles > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
     auto kern = dkdv_kernel<DT, D, KS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-        return NA2D_ERR_CUDA;
-    const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 512, C::SMEM, st>>>(tk, tv, tq, tg, tdk, tdv, lse, delta, (DT*)d_k, (DT*)d_v, g, tiles_r, tiles_c,
-                                     (int)tiles);
-    *launched += 1;
+    static std::atomic<unsigned long long> opted{0};
+    if (opt_in_smem(kern, C::SMEM, lc.device, opted) != cudaSuccess) return NA2D_ERR_CUDA;
+    const int grid = (int)(tiles < sm_count(lc.device) ? tiles : sm_count(lc.device));
+    kern<<<grid, 512, C::SMEM, lc.st>>>(tk, tv, tq, tg, tdk, tdv, lse, delta, lc.err_word, g, tiles_r, tiles_c,
+                                        (int)tiles);
+    *lc.launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
-}
-
-inline int backward_dkdv(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-                         const void* d_o, const float* delta, void* d_k, void* d_v, int device, cudaStream_t st,
-                         int* launched) {
-    if (dtype == NA2D_BF16) {
-        NA2D_TC_DISPATCH_D(launch_dkdv, __nv_bfloat16, g, dtype, q, k, v, lse, d_o, delta, d_k, d_v, device, st, launched)
-    } else {
-        NA2D_TC_DISPATCH_D(launch_dkdv, __half, g, dtype, q, k, v, lse, d_o, delta, d_k, d_v, device, st, launched)
-    }
 }
 
 }  // namespace na2d_tc

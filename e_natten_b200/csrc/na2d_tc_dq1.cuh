@@ -18,18 +18,6 @@
 
 namespace na2d_tc {
 
-// Low and high 64 bits of the mask with bit r * hw set for r < rc (rc * hw <= 128).
-constexpr unsigned long long row_repeat_lo(int hw, int rc) {
-    unsigned long long m = 0;
-    for (int r = 0; r < rc; ++r) if (r * hw < 64) m |= 1ull << (r * hw);
-    return m;
-}
-constexpr unsigned long long row_repeat_hi(int hw, int rc) {
-    unsigned long long m = 0;
-    for (int r = 0; r < rc; ++r) if (r * hw >= 64) m |= 1ull << (r * hw - 64);
-    return m;
-}
-
 template <int D, int KS, bool SPLIT>
 struct Dq1Cfg : Cfg<D, KS, 128, 0, 2> {
     using B = Cfg<D, KS, 128, 0, 2>;
@@ -44,25 +32,13 @@ struct Dq1Cfg : Cfg<D, KS, 128, 0, 2> {
     static_assert(B::NKP <= 128 && D <= 128, "tensor memory layout");
 };
 
-// 128-bit helpers on (lo, hi) pairs.
-__device__ __forceinline__ void shl128(unsigned long long& lo, unsigned long long& hi, int s) {   // 0 <= s < 64
-    if (s > 0) {
-        hi = (hi << s) | (lo >> (64 - s));
-        lo <<= s;
-    }
-}
-// Bits [0, k) set, 0 <= k <= 128.
-__device__ __forceinline__ void low_bits128(int k, unsigned long long& lo, unsigned long long& hi) {
-    lo = k >= 64 ? ~0ull : ((1ull << k) - 1ull);
-    hi = k >= 128 ? ~0ull : (k > 64 ? ((1ull << (k - 64)) - 1ull) : 0ull);
-}
-
 template <typename DT, int D, int KS>
 __global__ void __launch_bounds__(384, 1)
 dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
            const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
            const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse, float* __restrict__ delta,
-           const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
+           unsigned int* __restrict__ err_word, const Na2dGeom g, const int tiles_r, const int tiles_c,
+           const int total_tiles) {
     constexpr bool SPLIT = IsBf16<DT>::value;
     using C = Dq1Cfg<D, KS, SPLIT>;
     extern __shared__ uint8_t smem_raw[];
@@ -83,6 +59,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     uint64_t* st_empty = bars + 12;          // [4]  MMA (commit) -> TMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -129,13 +106,16 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    auto decode = [&](int i, int& bn, int& r0, int& c0) {
+    // my i-th tile: unit bn = head hn of batch hb, first row r0, first column c0
+    auto decode = [&](int i, int& bn, int& hn, int& hb, int& r0, int& c0) {
         int t = (int)blockIdx.x + i * (int)gridDim.x;
         const int tc = t % tiles_c;
         t /= tiles_c;
         r0 = (t % tiles_r) * TH;
         c0 = tc * TW;
         bn = t / tiles_r;
+        hb = bn / g.N;
+        hn = bn - hb * g.N;
     };
     // Strip buffers of tile i: every tile the roles rotate (K_A, V_A, K_B, V_B) <- (V_A, V_B, K_A, K_B),
     // a cycle of length four.  Each buffer is filled and released exactly once per tile, so the
@@ -152,33 +132,38 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         // ------------------------------------------------------------------ producer
         reg_dec<kRegsDonor>();
         if (lane == 0) {
-            for (int i = 0; i < n_my; ++i) {
-                int bn, r0, c0;
-                decode(i, bn, r0, c0);
+            LoadTracker<5> lt;                                   // slots: strip buffers 0-3, Q / dO tile 4
+            for (int i = 0; i < n_my && lt.ok; ++i) {
+                int bn, hn, hb, r0, c0;
+                decode(i, bn, hn, hb, r0, c0);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
                 const Slots s = slots_of(i);
                 const uint32_t par_free = (i & 1) ^ 1;
-                mbar_wait(q_empty, par_free, abort_flag, kErrLoadWait);
-                mbar_expect_tx(q_full, 2u * C::Q_BYTES);
+                if (!lt.acquire(q_empty, par_free, wctx)) break;
+                lt.arm(4, q_full, i & 1, 2u * C::Q_BYTES);
 #pragma unroll
                 for (int sl = 0; sl < C::NS; ++sl) {
-                    tma_load_4d(sQ + sl * C::Q_SLAB, &tm_q, q_full, sl * 64, c0, r0, bn);
-                    tma_load_4d(sDO + sl * C::Q_SLAB, &tm_do, q_full, sl * 64, c0, r0, bn);
+                    tma_load_5d(sQ + sl * C::Q_SLAB, &tm_q, q_full, sl * 64, c0, r0, hn, hb);
+                    tma_load_5d(sDO + sl * C::Q_SLAB, &tm_do, q_full, sl * 64, c0, r0, hn, hb);
                 }
                 // K_A, V_A first: their buffers were released by the previous tile's score MMAs
                 const int slot[4] = {s.ka, s.va, s.kb, s.vb};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    mbar_wait(st_empty + slot[j], par_free, abort_flag, kErrLoadWait);
-                    mbar_expect_tx(st_full + slot[j], (uint32_t)C::NS * C::NK * C::ROWB);
-                    const CUtensorMap* map = (j & 1) ? &tm_v : &tm_k;
+                    if (!lt.acquire(st_empty + slot[j], par_free, wctx)) break;
+                    lt.arm(slot[j], st_full + slot[j], i & 1, (uint32_t)C::NS * C::NK * C::ROWB);
                     uint8_t* dst = sStrip + slot[j] * C::KV_BYTES;
+                    // (the tensor map is named in each call: a map chosen through a run-time pointer
+                    // may be copied to local memory, where TMA cannot read it)
 #pragma unroll
-                    for (int sl = 0; sl < C::NS; ++sl)
-                        tma_load_4d(dst + sl * C::KV_SLAB, map, st_full + slot[j], sl * 64, box_c0 + (j >> 1) * C::HW, box_r0, bn);
+                    for (int sl = 0; sl < C::NS; ++sl) {
+                        if (j & 1) tma_load_5d(dst + sl * C::KV_SLAB, &tm_v, st_full + slot[j], sl * 64, box_c0 + (j >> 1) * C::HW, box_r0, hn, hb);
+                        else tma_load_5d(dst + sl * C::KV_SLAB, &tm_k, st_full + slot[j], sl * 64, box_c0 + (j >> 1) * C::HW, box_r0, hn, hb);
+                    }
                 }
             }
+            lt.drain(wctx);
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
@@ -197,10 +182,10 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const Slots s = slots_of(i);
             const int sk = x ? s.kb : s.ka, sv = x ? s.vb : s.va;
             const uint32_t par = i & 1;
-            if (x == 0) mbar_wait(q_full, par, abort_flag, kErrLoadWait);
-            mbar_wait(st_full + sk, par, abort_flag, kErrLoadWait);
-            mbar_wait(st_full + sv, par, abort_flag, kErrLoadWait);
-            if (x == 1) mbar_wait(dq_free, par ^ 1, abort_flag, kErrMmaWait);     // dQ of tile i - 1 sits over S_B
+            if (x == 0) mbar_wait(q_full, par, wctx, kErrLoadWait);
+            mbar_wait(st_full + sk, par, wctx, kErrLoadWait);
+            mbar_wait(st_full + sv, par, wctx, kErrLoadWait);
+            if (x == 1) mbar_wait(dq_free, par ^ 1, wctx, kErrMmaWait);     // dQ of tile i - 1 sits over S_B
             tc_fence_after();
             const uint32_t k_lo = smem_desc_lo(strip_base + sk * C::KV_BYTES, 16);
             const uint32_t v_lo = smem_desc_lo(strip_base + sv * C::KV_BYTES, 16);
@@ -227,7 +212,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         auto outputs = [&](int i, int x) {
             const Slots s = slots_of(i);
             const int sk = x ? s.kb : s.ka;
-            mbar_wait(p_full + x, i & 1, abort_flag, kErrMmaWait);
+            mbar_wait(p_full + x, i & 1, wctx, kErrMmaWait);
             tc_fence_after();
             const uint32_t km_lo = smem_desc_lo(strip_base + sk * C::KV_BYTES, C::KV_SLAB);
             const uint32_t t_ds = tmem_base + (x ? C::TMEM_DPB : C::TMEM_DPA);
@@ -277,8 +262,8 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         constexpr unsigned long long kRepLo = C::REP_LO, kRepHi = C::REP_HI;   // bit r * HW for the ks window rows
 
         for (int i = 0; i < n_my; ++i) {
-            int bn, r0, c0;
-            decode(i, bn, r0, c0);
+            int bn, hn, hb, r0, c0;
+            decode(i, bn, hn, hb, r0, c0);
             const uint32_t par = i & 1;
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
@@ -324,7 +309,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     }
                 }
                 if (tid == 0) NA2D_TR(3, x ? 2 : 0, i);
-                mbar_wait(s_full + x, par, abort_flag, kErrMmaWait);
+                mbar_wait(s_full + x, par, wctx, kErrMmaWait);
                 tc_fence_after();
                 if (tid == 0) NA2D_TR(3, x ? 3 : 1, i);
 #pragma unroll
@@ -349,8 +334,8 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                         for (int e = 0; e < 16; e += 2) {
                             const bool ok0 = (vmask[x][a] >> e) & 1u, ok1 = (vmask[x][a] >> (e + 1)) & 1u;
-                            const float p0 = ok0 ? fast_exp2(fmaf(__uint_as_float(s[x][a][e]), kLog2e, -lse2)) : 0.f;
-                            const float p1 = ok1 ? fast_exp2(fmaf(__uint_as_float(s[x][a][e + 1]), kLog2e, -lse2)) : 0.f;
+                            const float p0 = ok0 ? fast_exp2(fmaf(__uint_as_float(s[x][a][e]), g.sl2, -lse2)) : 0.f;
+                            const float p1 = ok1 ? fast_exp2(fmaf(__uint_as_float(s[x][a][e + 1]), g.sl2, -lse2)) : 0.f;
                             s[x][a][e] = __float_as_uint(p0);
                             s[x][a][e + 1] = __float_as_uint(p1);
                             // masked columns may hold anything: keep them out by selection, never by
@@ -370,6 +355,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             bar_sync(1 + quarter, 64);
             const float dl = (d0 + d1) + x_sum[(par * 2 + (half ^ 1)) * 128 + row];
             if (q_valid && half == 0) delta[qi] = dl;
+            const float dls = dl * g.scale;                  // dS carries the softmax scale: dQ = scale * sum_j p (dP - delta) k
 
             // dS = p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path)
 #pragma unroll
@@ -383,8 +369,8 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                         for (int e2 = 0; e2 < 8; ++e2) {
                             // p and dP of masked columns are exact zeros here
-                            const float ds0 = __uint_as_float(s[x][a][2 * e2]) * (__uint_as_float(dp[x][a][2 * e2]) - dl);
-                            const float ds1 = __uint_as_float(s[x][a][2 * e2 + 1]) * (__uint_as_float(dp[x][a][2 * e2 + 1]) - dl);
+                            const float ds0 = __uint_as_float(s[x][a][2 * e2]) * fmaf(__uint_as_float(dp[x][a][2 * e2]), g.scale, -dls);
+                            const float ds1 = __uint_as_float(s[x][a][2 * e2 + 1]) * fmaf(__uint_as_float(dp[x][a][2 * e2 + 1]), g.scale, -dls);
                             wd[e2] = pack2<DT>(ds0, ds1);
                             wr2[e2] = SPLIT ? pack2_residual_bf16(ds0, ds1, wd[e2]) : 0u;
                         }
@@ -411,7 +397,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             }
 
             // ---- epilogue: this half's columns of the dQ rows of the warp's 32 queries
-            mbar_wait(dq_full, par, abort_flag, kErrMmaWait);
+            mbar_wait(dq_full, par, wctx, kErrMmaWait);
             tc_fence_after();
             uint32_t acc[DH];
 #pragma unroll
@@ -422,7 +408,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) mbar_arrive(dq_free);
             if (tid == 0) NA2D_TR(3, 7, i);
-            stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0, r0 + quarter * (32 / TW), bn,
+            stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0, r0 + quarter * (32 / TW), hn, hb,
                                     lane);
         }
         if (lane == 0) bulk_wait<0>();          // the staging buffer has been read, the rows written
@@ -437,25 +423,26 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 }
 
 template <typename DT, int D, int KS>
-int launch_dq1(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, const float* lse,
-               const void* d_o, void* d_q, float* delta, int device, cudaStream_t st, int* launched) {
+int launch_dq1(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, const TensorArg& v, const float* lse,
+               const TensorArg& d_o, const TensorArg& d_q, float* delta) {
     using C = Dq1Cfg<D, KS, IsBf16<DT>::value>;
+    const Na2dGeom& g = lc.g;
     CUtensorMap tq, tg, tk, tv, tdq;
-    int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tdq, d_q, dtype, g.BN, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
-    if (rc == NA2D_OK) rc = make_map(&tg, d_o, dtype, g.BN, g.Hq, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
-    if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
+    int rc = make_map(&tq, q, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&tdq, d_q, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
+    if (rc == NA2D_OK) rc = make_map(&tg, d_o, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&tk, k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, C::HW, C::RC);
+    if (rc == NA2D_OK) rc = make_map(&tv, v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc != NA2D_OK) return rc;
     const int tiles_r = (g.Hq + TH - 1) / TH, tiles_c = (g.W + TW - 1) / TW;
     const long long tiles = (long long)g.BN * tiles_r * tiles_c;
     if (tiles > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
     auto kern = dq1_kernel<DT, D, KS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-        return NA2D_ERR_CUDA;
-    const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 384, C::SMEM, st>>>(tq, tg, tk, tv, tdq, lse, delta, g, tiles_r, tiles_c, (int)tiles);
-    *launched += 1;
+    static std::atomic<unsigned long long> opted{0};
+    if (opt_in_smem(kern, C::SMEM, lc.device, opted) != cudaSuccess) return NA2D_ERR_CUDA;
+    const int grid = (int)(tiles < sm_count(lc.device) ? tiles : sm_count(lc.device));
+    kern<<<grid, 384, C::SMEM, lc.st>>>(tq, tg, tk, tv, tdq, lse, delta, lc.err_word, g, tiles_r, tiles_c, (int)tiles);
+    *lc.launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }
 

@@ -59,7 +59,7 @@ template <typename DT, int D, int KS>
 __global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-           float* __restrict__ lse,
+           float* __restrict__ lse, unsigned int* __restrict__ err_word,
            const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
     using C = FwdCfg<D, KS>;
     constexpr int NSTK = C::NSTK, NSTV = C::NSTV, NQ = C::NQ;
@@ -85,6 +85,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     uint64_t* pv_done = bars + 18;           //       MMA (commit) -> softmax: O holds this chunk
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -132,13 +133,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    auto decode = [&](int i, int& bn, int& r0, int& c0) {
+    // my i-th tile: unit bn = head hn of batch hb, first row r0, first column c0
+    auto decode = [&](int i, int& bn, int& hn, int& hb, int& r0, int& c0) {
         int t = (int)blockIdx.x + i * (int)gridDim.x;
         const int tc = t % tiles_c;
         t /= tiles_c;
         r0 = (t % tiles_r) * TH;
         c0 = tc * TW;
         bn = t / tiles_r;
+        hb = bn / g.N;
+        hn = bn - hb * g.N;
     };
 
     if (warp == 8) {
@@ -146,36 +150,38 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         reg_dec<kRegsDonor>();
         if (lane == 0) {
             uint32_t n = 0;
-            for (int i = 0; i < n_my; ++i) {
-                int bn, r0, c0;
-                decode(i, bn, r0, c0);
+            LoadTracker<6> lt;                                  // slots: Q 0-1, K 2-3, V 4-5
+            for (int i = 0; i < n_my && lt.ok; ++i) {
+                int bn, hn, hb, r0, c0;
+                decode(i, bn, hn, hb, r0, c0);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
                 const int qb = i % NQ;
-                mbar_wait(q_empty + qb, ((i / NQ) & 1) ^ 1, abort_flag, kErrLoadWait);
-                mbar_expect_tx(q_full + qb, C::Q_BYTES);
+                if (!lt.acquire(q_empty + qb, ((i / NQ) & 1) ^ 1, wctx)) break;
+                lt.arm(qb, q_full + qb, (i / NQ) & 1, C::Q_BYTES);
 #pragma unroll
                 for (int s = 0; s < C::NS; ++s)
-                    tma_load_4d(sQ + qb * C::Q_BYTES + s * C::Q_SLAB, &tm_q, q_full + qb, s * 64, c0, r0, bn);
+                    tma_load_5d(sQ + qb * C::Q_BYTES + s * C::Q_SLAB, &tm_q, q_full + qb, s * 64, c0, r0, hn, hb);
                 for (int c = 0; c < C::NCH; ++c, ++n) {
                     const uint32_t sk = n % NSTK, sv = n % NSTV;
                     NA2D_TR(1, 0, n);
-                    mbar_wait(k_empty + sk, ((n / NSTK) & 1) ^ 1, abort_flag, kErrLoadWait);
+                    if (!lt.acquire(k_empty + sk, ((n / NSTK) & 1) ^ 1, wctx)) break;
                     NA2D_TR(1, 1, n);
-                    mbar_expect_tx(k_full + sk, (uint32_t)C::NS * C::NK * C::ROWB);
+                    lt.arm(2 + sk, k_full + sk, (n / NSTK) & 1, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
-                        tma_load_4d(sK + sk * C::K_BYTES + s * C::K_SLAB, &tm_k, k_full + sk, s * 64, box_c0,
-                                    box_r0 + c * C::RC, bn);
-                    mbar_wait(v_empty + sv, ((n / NSTV) & 1) ^ 1, abort_flag, kErrLoadWait);
+                        tma_load_5d(sK + sk * C::K_BYTES + s * C::K_SLAB, &tm_k, k_full + sk, s * 64, box_c0,
+                                    box_r0 + c * C::RC, hn, hb);
+                    if (!lt.acquire(v_empty + sv, ((n / NSTV) & 1) ^ 1, wctx)) break;
                     NA2D_TR(1, 2, n);
-                    mbar_expect_tx(v_full + sv, (uint32_t)C::NS * C::NK * C::ROWB);
+                    lt.arm(4 + sv, v_full + sv, (n / NSTV) & 1, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
-                        tma_load_4d(sV + sv * C::V_BYTES + s * C::KV_SLAB, &tm_v, v_full + sv, s * 64, box_c0,
-                                    box_r0 + c * C::RC, bn);
+                        tma_load_5d(sV + sv * C::V_BYTES + s * C::KV_SLAB, &tm_v, v_full + sv, s * 64, box_c0,
+                                    box_r0 + c * C::RC, hn, hb);
                 }
             }
+            lt.drain(wctx);
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
@@ -187,8 +193,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (uint32_t n = 0; n < total_units; ++n) {
             const uint32_t i = n / C::NCH, c = n % C::NCH, sk = n % NSTK, sv = n % NSTV, qb = i % NQ, ob = i & 1;
             if (lane == 0) NA2D_TR(2, 0, n);
-            if (c == 0) mbar_wait(q_full + qb, (i / NQ) & 1, abort_flag, kErrLoadWait);
-            mbar_wait(k_full + sk, (n / NSTK) & 1, abort_flag, kErrLoadWait);
+            if (c == 0) mbar_wait(q_full + qb, (i / NQ) & 1, wctx, kErrLoadWait);
+            mbar_wait(k_full + sk, (n / NSTK) & 1, wctx, kErrLoadWait);
             if (lane == 0) NA2D_TR(2, 1, n);
             tc_fence_after();
             const uint32_t q_lo = smem_desc_lo(smem_u32(sQ + qb * C::Q_BYTES), 16);
@@ -207,10 +213,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             }
             __syncwarp();
             if (lane == 0) NA2D_TR(2, 2, n);
-            mbar_wait(v_full + sv, (n / NSTV) & 1, abort_flag, kErrLoadWait);
-            mbar_wait(p_full, n & 1, abort_flag, kErrMmaWait);
+            mbar_wait(v_full + sv, (n / NSTV) & 1, wctx, kErrLoadWait);
+            mbar_wait(p_full, n & 1, wctx, kErrMmaWait);
             if (lane == 0) NA2D_TR(2, 3, n);
-            if (c == 0) mbar_wait(o_free + ob, ((i >> 1) & 1) ^ 1, abort_flag, kErrMmaWait);
+            if (c == 0) mbar_wait(o_free + ob, ((i >> 1) & 1) ^ 1, wctx, kErrMmaWait);
             tc_fence_after();
             const uint32_t v_lo = smem_desc_lo(smem_u32(sV + sv * C::V_BYTES), C::KV_SLAB);
             if (elect_one()) {
@@ -241,13 +247,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         uint32_t pend_tile = 0;
         float pend_max = 0.f, pend_sum = 1.f;
         size_t pend_qi = 0;
-        int pend_bn = 0, pend_r0 = 0, pend_c0 = 0;
+        int pend_hn = 0, pend_hb = 0, pend_r0 = 0, pend_c0 = 0;
 
         auto epilogue = [&]() {
             const uint32_t ob = pend_tile & 1;
             bar_sync(1 + quarter, 64);                                       // partner's row sum is in x_sum
             const float total = pend_sum + x_sum[((pend_tile & 1) * 2 + (half ^ 1)) * 128 + row];
-            mbar_wait(o_full + ob, (pend_tile >> 1) & 1, abort_flag, kErrMmaWait);
+            mbar_wait(o_full + ob, (pend_tile >> 1) & 1, wctx, kErrMmaWait);
             tc_fence_after();
             const float inv = 1.f / total;
             uint32_t acc[DH];
@@ -260,15 +266,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) mbar_arrive(o_free + ob);                         // O is in registers
             stage_and_store<DT, DH>(&tm_o, sOut + warp * OutStage<DH>::BYTES, acc, inv, half * DH, pend_c0,
-                                    pend_r0 + quarter * (32 / TW), pend_bn, lane);
+                                    pend_r0 + quarter * (32 / TW), pend_hn, pend_hb, lane);
             if (pend_valid && half == 0) lse[pend_qi] = (pend_max + log2f(total)) * kLn2;
             pend = false;
         };
 
         uint32_t n = 0;
         for (int i = 0; i < n_my; ++i) {
-            int bn, r0, c0;
-            decode(i, bn, r0, c0);
+            int bn, hn, hb, r0, c0;
+            decode(i, bn, hn, hb, r0, c0);
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
             const int qr_raw = r0 + (row / TW), qc_raw = c0 + (row % TW);
@@ -276,8 +282,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const int qr = min(qr_raw, g.Hq - 1), qc = min(qc_raw, g.W - 1);
             const int wr = na2d_ws(g.q_row0 + qr, g.Hg, KS) - g.kv_row0 - box_r0;   // in [0, TH)
             const int wc = na2d_ws(qc, g.W, KS) - box_c0;                            // in [0, TW)
-            const uint32_t row_mask = ((1u << KS) - 1u) << wr;
-            const uint32_t col_mask = ((1u << KS) - 1u) << wc;
             const int wr_lo = __shfl_sync(0xffffffffu, wr, 0);
             const int wr_hi = __shfl_sync(0xffffffffu, wr, 31);
             const uint32_t o_addr = tmem_lane + C::TMEM_O0 + (i & 1) * C::TMEM_OSTRIDE + half * DH;
@@ -299,7 +303,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 const int b_hi = (max(j_hi, 0) + 15) >> 4;                                   // blocks [j_lo/16, b_hi)
                 const int bi_lo = ((j_lo >> 4) - half + 1) >> 1;                             // first own block in range
                 if (tid == 0) NA2D_TR(3, 0, n);
-                mbar_wait(s_full, n & 1, abort_flag, kErrMmaWait);
+                mbar_wait(s_full, n & 1, wctx, kErrMmaWait);
                 if (tid == 0) NA2D_TR(3, 1, n);
                 tc_fence_after();
 
@@ -314,16 +318,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                 for (int t = 0; t < NACT; ++t) {
                     const int blk = half + 2 * (bi_lo + t);
-                    uint32_t m = 0;
-#pragma unroll
-                    for (int u = 0; u < KS; ++u) {
-                        const int r = wr + u - row_off;                    // chunk row of window row u
-                        const int rel = r * C::HW + wc - 16 * blk;         // its first column, relative to the block
-                        const uint32_t seg = (1u << KS) - 1u;
-                        const uint32_t bits = rel >= 0 ? (seg << (rel & 31)) : (seg >> ((-rel) & 31));
-                        if (r >= 0 && r < C::RC && rel > -KS && rel < 16) m |= bits;
-                    }
-                    vmask[t] = (blk < b_hi) ? (m & 0xffffu) : 0u;
+                    vmask[t] = (blk < b_hi) ? block_mask16<C::HW, KS, C::RC>(blk, wr - row_off, wc) : 0u;
                 }
                 tmem_ld_wait();
                 if (tid == 0) NA2D_TR(3, 2, n);
@@ -346,13 +341,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 // This barrier also orders the partner's reads of S before this thread's writes of P,
                 // which land in the same tensor-memory columns.
                 bar_sync(1 + quarter, 64);
-                cmax = fmaxf(cmax, x_max[((n & 1) * 2 + (half ^ 1)) * 128 + row]) * kLog2e;
+                cmax = fmaxf(cmax, x_max[((n & 1) * 2 + (half ^ 1)) * 128 + row]) * g.sl2;
 
                 // Raise the running maximum only when it would grow by more than the step; a row
                 // whose maximum is still -inf has an all-zero O row and takes the new one freely.
                 const bool grow = cmax > run_max + kRescaleStep;
                 if (C::NCH > 1 && ch > 0) {
-                    mbar_wait(pv_done, (n & 1) ^ 1, abort_flag, kErrMmaWait);     // O holds the previous chunk
+                    mbar_wait(pv_done, (n & 1) ^ 1, wctx, kErrMmaWait);     // O holds the previous chunk
                     if (__any_sync(0xffffffffu, grow && run_max != -CUDART_INF_F)) {
                         const float alpha = grow ? fast_exp2(run_max - cmax) : 1.f;
                         tc_fence_after();
@@ -385,8 +380,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                         uint32_t w[8];
 #pragma unroll
                         for (int e2 = 0; e2 < 8; ++e2) {
-                            const float e0 = fast_exp2(fmaf(__uint_as_float(s[t][2 * e2]), kLog2e, -safe_max));
-                            const float e1 = fast_exp2(fmaf(__uint_as_float(s[t][2 * e2 + 1]), kLog2e, -safe_max));
+                            const float e0 = fast_exp2(fmaf(__uint_as_float(s[t][2 * e2]), g.sl2, -safe_max));
+                            const float e1 = fast_exp2(fmaf(__uint_as_float(s[t][2 * e2 + 1]), g.sl2, -safe_max));
                             const float p0 = ((vmask[t] >> (2 * e2)) & 1u) ? e0 : 0.f;
                             const float p1 = ((vmask[t] >> (2 * e2 + 1)) & 1u) ? e1 : 0.f;
                             c0s += p0;
@@ -422,7 +417,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             x_sum[((i & 1) * 2 + half) * 128 + row] = run_sum;
             pend = true;
             pend_tile = (uint32_t)i;
-            pend_bn = bn;
+            pend_hn = hn;
+            pend_hb = hb;
             pend_r0 = r0;
             pend_c0 = c0;
             pend_valid = q_valid;
@@ -443,35 +439,30 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 }
 
 template <typename DT, int D, int KS>
-int launch_forward(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
-                   int device, cudaStream_t st, int* launched) {
+int launch_forward(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, const TensorArg& v, const TensorArg& o,
+                   float* lse) {
     // kernel sizes 3 and 5 go to the strip kernel
-    if constexpr (KS <= 5) return launch_forward1<DT, D, KS>(g, dtype, q, k, v, o, lse, device, st, launched);
+    if constexpr (KS <= 5) {
+        return launch_forward1<DT, D, KS>(lc, q, k, v, o, lse);
+    } else {
     using C = FwdCfg<D, KS>;
+    const Na2dGeom& g = lc.g;
     CUtensorMap tq, tk, tv, to;
-    int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&to, o, dtype, g.BN, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
-    if (rc == NA2D_OK) rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
-    if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
+    int rc = make_map(&tq, q, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&to, o, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, 32 / TW, OutStage<D / 2>::RW);
+    if (rc == NA2D_OK) rc = make_map(&tk, k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, C::HW, C::RC);
+    if (rc == NA2D_OK) rc = make_map(&tv, v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc != NA2D_OK) return rc;
     const int tiles_r = (g.Hq + TH - 1) / TH, tiles_c = (g.W + TW - 1) / TW;
     const long long tiles = (long long)g.BN * tiles_r * tiles_c;
     if (tiles > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
     auto kern = fwd_kernel<DT, D, KS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-        return NA2D_ERR_CUDA;
-    const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 384, C::SMEM, st>>>(tq, tk, tv, to, lse, g, tiles_r, tiles_c, (int)tiles);
-    *launched += 1;
+    static std::atomic<unsigned long long> opted{0};
+    if (opt_in_smem(kern, C::SMEM, lc.device, opted) != cudaSuccess) return NA2D_ERR_CUDA;
+    const int grid = (int)(tiles < sm_count(lc.device) ? tiles : sm_count(lc.device));
+    kern<<<grid, 384, C::SMEM, lc.st>>>(tq, tk, tv, to, lse, lc.err_word, g, tiles_r, tiles_c, (int)tiles);
+    *lc.launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
-}
-
-inline int forward(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
-                   int device, cudaStream_t st, int* launched) {
-    if (dtype == NA2D_BF16) {
-        NA2D_TC_DISPATCH_D(launch_forward, __nv_bfloat16, g, dtype, q, k, v, o, lse, device, st, launched)
-    } else {
-        NA2D_TC_DISPATCH_D(launch_forward, __half, g, dtype, q, k, v, o, lse, device, st, launched)
     }
 }
 

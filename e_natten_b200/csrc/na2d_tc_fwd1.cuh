@@ -37,7 +37,8 @@ template <typename DT, int D, int KS>
 __global__ void __launch_bounds__(512, 1)
 fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
             const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-            float* __restrict__ lse, const Na2dGeom g, const int tiles_r, const int tiles_c, const int total_tiles) {
+            float* __restrict__ lse, unsigned int* __restrict__ err_word, const Na2dGeom g, const int tiles_r,
+            const int tiles_c, const int total_tiles) {
     using C = Fwd1Cfg<D, KS>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -58,6 +59,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     uint64_t* kv_empty = bars + 12;          // [4]  MMA (commit) -> TMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -102,13 +104,16 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    auto decode = [&](int i, int& bn, int& r0, int& c0) {
+    // my i-th tile: unit bn = head hn of batch hb, first row r0, first column c0
+    auto decode = [&](int i, int& bn, int& hn, int& hb, int& r0, int& c0) {
         int t = (int)blockIdx.x + i * (int)gridDim.x;
         const int tc = t % tiles_c;
         t /= tiles_c;
         r0 = (t % tiles_r) * TH;
         c0 = tc * TW;
         bn = t / tiles_r;
+        hb = bn / g.N;
+        hn = bn - hb * g.N;
     };
     // strip buffer of strip x of tile i: tile i uses (2i) % 3 and (2i + 1) % 3
     auto strip_col = [](int i, int x) { return ((2 * i + x) % 3) * C::TMEM_STRIP; };
@@ -121,33 +126,36 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
             const int j0 = warp == 8 ? 0 : 2;
+            LoadTracker<3> lt;                                          // slots: K_A / V_A, K_B / V_B, Q
             for (int i = 0; i < n_my; ++i) {
-                int bn, r0, c0;
-                decode(i, bn, r0, c0);
+                int bn, hn, hb, r0, c0;
+                decode(i, bn, hn, hb, r0, c0);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
                 const uint32_t par_free = (i & 1) ^ 1;
                 if (warp == 8) {
-                    mbar_wait(q_empty, par_free, abort_flag, kErrLoadWait);
-                    mbar_expect_tx(q_full, (uint32_t)C::Q_BYTES);
+                    if (!lt.acquire(q_empty, par_free, wctx)) break;
+                    lt.arm(2, q_full, i & 1, (uint32_t)C::Q_BYTES);
 #pragma unroll
-                    for (int sl = 0; sl < C::NS; ++sl) tma_load_4d(sQ + sl * C::Q_SLAB, &tm_q, q_full, sl * 64, c0, r0, bn);
+                    for (int sl = 0; sl < C::NS; ++sl) tma_load_5d(sQ + sl * C::Q_SLAB, &tm_q, q_full, sl * 64, c0, r0, hn, hb);
                 }
                 // (the tensor map is named in each call: a map chosen through a run-time pointer
                 // may be copied to local memory, where TMA cannot read it)
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     const int j = j0 + x;                               // K_A, K_B or V_A, V_B
-                    mbar_wait(kv_empty + j, par_free, abort_flag, kErrLoadWait);
-                    mbar_expect_tx(kv_full + j, (uint32_t)C::NS * C::NK * C::ROWB);
+                    if (!lt.acquire(kv_empty + j, par_free, wctx)) break;
+                    lt.arm(x, kv_full + j, i & 1, (uint32_t)C::NS * C::NK * C::ROWB);
                     uint8_t* dst = sKV + j * C::KV_BYTES;
 #pragma unroll
                     for (int sl = 0; sl < C::NS; ++sl) {
-                        if (warp == 8) tma_load_4d(dst + sl * C::KV_SLAB, &tm_k, kv_full + j, sl * 64, box_c0 + x * C::HW, box_r0, bn);
-                        else tma_load_4d(dst + sl * C::KV_SLAB, &tm_v, kv_full + j, sl * 64, box_c0 + x * C::HW, box_r0, bn);
+                        if (warp == 8) tma_load_5d(dst + sl * C::KV_SLAB, &tm_k, kv_full + j, sl * 64, box_c0 + x * C::HW, box_r0, hn, hb);
+                        else tma_load_5d(dst + sl * C::KV_SLAB, &tm_v, kv_full + j, sl * 64, box_c0 + x * C::HW, box_r0, hn, hb);
                     }
                 }
+                if (!lt.ok) break;
             }
+            lt.drain(wctx);
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
@@ -162,8 +170,8 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
         auto scores = [&](int i, int x) {
             const uint32_t par = i & 1;
-            if (x == 0) mbar_wait(q_full, par, abort_flag, kErrLoadWait);
-            mbar_wait(kv_full + x, par, abort_flag, kErrLoadWait);
+            if (x == 0) mbar_wait(q_full, par, wctx, kErrLoadWait);
+            mbar_wait(kv_full + x, par, wctx, kErrLoadWait);
             tc_fence_after();
             const uint32_t k_lo = smem_desc_lo(kv_base + x * C::KV_BYTES, 16);
             const uint32_t t_s = tmem_base + strip_col(i, x);
@@ -185,9 +193,9 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         };
         auto outputs = [&](int i, int x) {
             const uint32_t par = i & 1;
-            mbar_wait(p_full + x, par, abort_flag, kErrMmaWait);
-            mbar_wait(kv_full + 2 + x, par, abort_flag, kErrLoadWait);
-            if (x == 0) mbar_wait(o_free, par ^ 1, abort_flag, kErrMmaWait);      // O of tile i - 1 has been read
+            mbar_wait(p_full + x, par, wctx, kErrMmaWait);
+            mbar_wait(kv_full + 2 + x, par, wctx, kErrLoadWait);
+            if (x == 0) mbar_wait(o_free, par ^ 1, wctx, kErrMmaWait);      // O of tile i - 1 has been read
             tc_fence_after();
             const uint32_t v_lo = smem_desc_lo(kv_base + (2 + x) * C::KV_BYTES, C::KV_SLAB);
             const uint32_t t_p = tmem_base + strip_col(i, x);
@@ -224,11 +232,11 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         uint8_t* stage = sOut + quarter * OutStage<32>::BYTES;
         constexpr int RPO = D / 32;                          // 32-channel rounds
         for (int i = 0; i < n_my; ++i) {
-            int bn, r0, c0;
-            decode(i, bn, r0, c0);
+            int bn, hn, hb, r0, c0;
+            decode(i, bn, hn, hb, r0, c0);
             const uint32_t par = i & 1;
             const int qr = r0 + (row / TW), qc = c0 + (row % TW);
-            mbar_wait(o_full, par, abort_flag, kErrMmaWait);            // also: the softmax warps' sums are written
+            mbar_wait(o_full, par, wctx, kErrMmaWait);            // also: the softmax warps' sums are written
             tc_fence_after();
             const float total = x_sum[(par * 2 + 0) * 128 + row] + x_sum[(par * 2 + 1) * 128 + row];
             const float fin = x_fin[par * 128 + row];
@@ -245,7 +253,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                     __syncwarp();
                     if (lane == 0) mbar_arrive(o_free);
                 }
-                stage_and_store<DT, 32>(&tm_o, stage, v[j & 1], inv, 32 * j, c0, r0 + quarter * (32 / TW), bn, lane);
+                stage_and_store<DT, 32>(&tm_o, stage, v[j & 1], inv, 32 * j, c0, r0 + quarter * (32 / TW), hn, hb, lane);
             }
             if (qr < g.Hq && qc < g.W)
                 lse[(static_cast<size_t>(bn) * g.Hq + qr) * g.W + qc] = (fin + log2f(total)) * kLn2;
@@ -264,8 +272,8 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         constexpr unsigned long long kRepLo = C::REP_LO, kRepHi = C::REP_HI;   // bit r * HW for the ks window rows
 
         for (int i = 0; i < n_my; ++i) {
-            int bn, r0, c0;
-            decode(i, bn, r0, c0);
+            int bn, hn, hb, r0, c0;
+            decode(i, bn, hn, hb, r0, c0);
             const uint32_t par = i & 1;
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
@@ -306,7 +314,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                     }
                 }
                 if (tid == 0) NA2D_TR(3, x ? 2 : 0, i);
-                mbar_wait(s_full + x, par, abort_flag, kErrMmaWait);
+                mbar_wait(s_full + x, par, wctx, kErrMmaWait);
                 tc_fence_after();
                 if (tid == 0) NA2D_TR(3, x ? 3 : 1, i);
 #pragma unroll
@@ -344,7 +352,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             // This barrier also orders the partner's reads of S before this thread's writes of P,
             // which land in the same tensor-memory columns.
             bar_sync(1 + quarter, 64);
-            cmax = fmaxf(cmax, x_max[(par * 2 + (half ^ 1)) * 128 + row]) * kLog2e;
+            cmax = fmaxf(cmax, x_max[(par * 2 + (half ^ 1)) * 128 + row]) * g.sl2;
             const float safe_max = (cmax == -CUDART_INF_F) ? 0.f : cmax;
 
             // P = exp2(s * log2e - max) as packed 16-bit pairs -> tensor memory (over S), row sum
@@ -359,8 +367,8 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                         uint32_t w[8];
 #pragma unroll
                         for (int e2 = 0; e2 < 8; ++e2) {
-                            const float e0 = fast_exp2(fmaf(__uint_as_float(s[x][a][2 * e2]), kLog2e, -safe_max));
-                            const float e1 = fast_exp2(fmaf(__uint_as_float(s[x][a][2 * e2 + 1]), kLog2e, -safe_max));
+                            const float e0 = fast_exp2(fmaf(__uint_as_float(s[x][a][2 * e2]), g.sl2, -safe_max));
+                            const float e1 = fast_exp2(fmaf(__uint_as_float(s[x][a][2 * e2 + 1]), g.sl2, -safe_max));
                             const float p0 = ((vmask[x][a] >> (2 * e2)) & 1u) ? e0 : 0.f;
                             const float p1 = ((vmask[x][a] >> (2 * e2 + 1)) & 1u) ? e1 : 0.f;
                             c0s += p0;
@@ -402,24 +410,25 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 }
 
 template <typename DT, int D, int KS>
-int launch_forward1(const Na2dGeom& g, int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
-                    int device, cudaStream_t st, int* launched) {
+int launch_forward1(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, const TensorArg& v, const TensorArg& o,
+                    float* lse) {
     using C = Fwd1Cfg<D, KS>;
+    const Na2dGeom& g = lc.g;
     CUtensorMap tq, tk, tv, to;
-    int rc = make_map(&tq, q, dtype, g.BN, g.Hq, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&to, o, dtype, g.BN, g.Hq, g.W, D, TW, 32 / TW, 32);
-    if (rc == NA2D_OK) rc = make_map(&tk, k, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
-    if (rc == NA2D_OK) rc = make_map(&tv, v, dtype, g.BN, g.Hkv, g.W, D, C::HW, C::RC);
+    int rc = make_map(&tq, q, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, TH);
+    if (rc == NA2D_OK) rc = make_map(&to, o, lc.dtype, lc.B, g.N, g.Hq, g.W, D, TW, 32 / TW, 32);
+    if (rc == NA2D_OK) rc = make_map(&tk, k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, C::HW, C::RC);
+    if (rc == NA2D_OK) rc = make_map(&tv, v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, C::HW, C::RC);
     if (rc != NA2D_OK) return rc;
     const int tiles_r = (g.Hq + TH - 1) / TH, tiles_c = (g.W + TW - 1) / TW;
     const long long tiles = (long long)g.BN * tiles_r * tiles_c;
     if (tiles > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
     auto kern = fwd1_kernel<DT, D, KS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-        return NA2D_ERR_CUDA;
-    const int grid = (int)(tiles < sm_count(device) ? tiles : sm_count(device));
-    kern<<<grid, 512, C::SMEM, st>>>(tq, tk, tv, to, lse, g, tiles_r, tiles_c, (int)tiles);
-    *launched += 1;
+    static std::atomic<unsigned long long> opted{0};
+    if (opt_in_smem(kern, C::SMEM, lc.device, opted) != cudaSuccess) return NA2D_ERR_CUDA;
+    const int grid = (int)(tiles < sm_count(lc.device) ? tiles : sm_count(lc.device));
+    kern<<<grid, 512, C::SMEM, lc.st>>>(tq, tk, tv, to, lse, lc.err_word, g, tiles_r, tiles_c, (int)tiles);
+    *lc.launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }
 

@@ -25,8 +25,16 @@ What follows which reference lines (paths inside the e_natten project):
                              algebraically equal to diag(P) - P P^T applied to dP
                              (e_natten/pytorch.py:33-43, 250-257, 277-288)
 
+* natten1d_pixel / _fwd / _bwd <- the 1D operator: e_natten/pytorch.py:46-156 (loop
+                             restatement), e_natten/triton.py:65-222 (kernels); same math on
+                             one axis, (B, N, T, C)
+* natten2d_qk / natten2d_av <- the unfused pair the reference's test and benchmark compare
+                             with (test.py:17-21, bench.py:23, 52-54): window scores and their
+                             application, window member j at row j // ks, column j % ks
+
 Layout everywhere: (B, N, H, W, C) = batch, heads, grid rows, grid cols, head dim
-(e_natten/triton.py:500).  No softmax scale is applied (e_natten/triton.py:280).
+(e_natten/triton.py:500).  The reference applies no softmax scale (e_natten/triton.py:280);
+``scale`` (default 1) multiplies the logits, as a caller-side ``q * scale`` would.
 """
 from __future__ import annotations
 
@@ -36,6 +44,7 @@ __all__ = [
     "window_start", "backward_window_start", "backward_window_end",
     "window_start_table", "natten2d_pixel", "natten2d_fwd", "natten2d_bwd",
     "natten2d_fwd_bwd", "round_inputs",
+    "natten1d_pixel", "natten1d_fwd", "natten1d_bwd", "natten2d_qk", "natten2d_av",
 ]
 
 
@@ -108,14 +117,14 @@ def _row_origins(Hq: int, kernel_size: int, rows):
                         dtype=torch.int64)
 
 
-def natten2d_fwd(q, k, v, kernel_size: int, acc_dtype=torch.float64, rows=None):
+def natten2d_fwd(q, k, v, kernel_size: int, acc_dtype=torch.float64, rows=None, scale: float = 1.0):
     """Forward.  Returns (o, lse) in ``acc_dtype``; lse = max + log(sum exp), natural log.
 
     Loops over the k*k window offsets; each step is one full-tensor gather + dot.
     """
     B, N, H, W, C = q.shape
     ks = kernel_size
-    q, k, v = q.to(acc_dtype), k.to(acc_dtype), v.to(acc_dtype)
+    q, k, v = q.to(acc_dtype) * scale, k.to(acc_dtype), v.to(acc_dtype)
     wsx, wsy = _row_origins(H, ks, rows), window_start_table(W, ks)
     s = torch.empty(ks * ks, B, N, H, W, dtype=acc_dtype)
     for u in range(ks):
@@ -132,7 +141,7 @@ def natten2d_fwd(q, k, v, kernel_size: int, acc_dtype=torch.float64, rows=None):
     return o, m + torch.log(l)
 
 
-def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=None, o=None):
+def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=None, o=None, scale: float = 1.0):
     """Backward in flash form.  Returns (dq, dk, dv) in ``acc_dtype``.
 
     p = exp(s - lse), delta = dO.O, dS = p*(dO.V - delta), dQ = sum dS*K,
@@ -151,7 +160,7 @@ def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=N
     Hkv = k.shape[2]
     ks = kernel_size
     q, k, v, d_o = (t.to(acc_dtype) for t in (q, k, v, d_o))
-    o_exact, lse = natten2d_fwd(q, k, v, ks, acc_dtype, rows)
+    o_exact, lse = natten2d_fwd(q, k, v, ks, acc_dtype, rows, scale)
     delta = (d_o * (o_exact if o is None else o.to(acc_dtype))).sum(-1)
     wsx, wsy = _row_origins(H, ks, rows), window_start_table(W, ks)
     dq = torch.zeros_like(q)
@@ -161,8 +170,8 @@ def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=N
         for w in range(ks):
             ku = _shifted(k, wsx, wsy, u, w)
             vu = _shifted(v, wsx, wsy, u, w)
-            p = torch.exp((q * ku).sum(-1) - lse)
-            ds = p * ((d_o * vu).sum(-1) - delta)
+            p = torch.exp(scale * (q * ku).sum(-1) - lse)
+            ds = scale * p * ((d_o * vu).sum(-1) - delta)
             dq += ds.unsqueeze(-1) * ku
             lin = ((wsx + u).unsqueeze(1) * W + (wsy + w).unsqueeze(0)).reshape(-1)
             dk.index_add_(2, lin, (ds.unsqueeze(-1) * q).view(B, N, H * W, C))
@@ -170,13 +179,78 @@ def natten2d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=N
     return dq, dk.view(B, N, Hkv, W, C), dv.view(B, N, Hkv, W, C)
 
 
-def natten2d_fwd_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=None, save_dtype=None):
+def natten2d_fwd_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, rows=None, save_dtype=None,
+                     scale: float = 1.0):
     """(o, lse, dq, dk, dv) in one call.  ``save_dtype``: dtype in which o is handed to the
     backward (the input dtype of a 16-bit path); None hands over the exact o."""
-    o, lse = natten2d_fwd(q, k, v, kernel_size, acc_dtype, rows)
+    o, lse = natten2d_fwd(q, k, v, kernel_size, acc_dtype, rows, scale)
     o_saved = None if save_dtype is None else o.to(save_dtype)
-    dq, dk, dv = natten2d_bwd(q, k, v, d_o, kernel_size, acc_dtype, rows, o=o_saved)
+    dq, dk, dv = natten2d_bwd(q, k, v, d_o, kernel_size, acc_dtype, rows, o=o_saved, scale=scale)
     return o, lse, dq, dk, dv
+
+
+# --------------------------------------------------------------------------- 1D operator
+def natten1d_pixel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel_size: int) -> torch.Tensor:
+    """Differentiable per-token loop on (B, N, T, C): for every token the kernel_size keys at
+    the clamped origin, one softmax row (e_natten/pytorch.py:78-83 without the tiling)."""
+    T = q.shape[2]
+    outs = []
+    for i in range(T):
+        o0 = window_start(i, T, kernel_size)
+        s = torch.matmul(q[:, :, i:i + 1, :], k[:, :, o0:o0 + kernel_size, :].transpose(-1, -2))
+        outs.append(torch.matmul(torch.softmax(s, dim=-1), v[:, :, o0:o0 + kernel_size, :]))
+    return torch.cat(outs, dim=2)
+
+
+def natten1d_fwd(q, k, v, kernel_size: int, acc_dtype=torch.float64, scale: float = 1.0):
+    """1D forward, vectorised over the window offsets.  Returns (o, lse) in ``acc_dtype``."""
+    T = q.shape[2]
+    q, k, v = q.to(acc_dtype) * scale, k.to(acc_dtype), v.to(acc_dtype)
+    ws = window_start_table(T, kernel_size)
+    s = torch.stack([(q * k.index_select(2, ws + u)).sum(-1) for u in range(kernel_size)])
+    m = s.max(dim=0).values
+    e = torch.exp(s - m)
+    l = e.sum(0)
+    o = sum((e[u] / l).unsqueeze(-1) * v.index_select(2, ws + u) for u in range(kernel_size))
+    return o, m + torch.log(l)
+
+
+def natten1d_bwd(q, k, v, d_o, kernel_size: int, acc_dtype=torch.float64, scale: float = 1.0):
+    """1D backward in flash form.  Returns (dq, dk, dv) in ``acc_dtype``."""
+    T = q.shape[2]
+    q, k, v, d_o = (t.to(acc_dtype) for t in (q, k, v, d_o))
+    o, lse = natten1d_fwd(q, k, v, kernel_size, acc_dtype, scale)
+    delta = (d_o * o).sum(-1)
+    ws = window_start_table(T, kernel_size)
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+    for u in range(kernel_size):
+        ku, vu = k.index_select(2, ws + u), v.index_select(2, ws + u)
+        p = torch.exp(scale * (q * ku).sum(-1) - lse)
+        ds = scale * p * ((d_o * vu).sum(-1) - delta)
+        dq += ds.unsqueeze(-1) * ku
+        dk.index_add_(2, ws + u, ds.unsqueeze(-1) * q)
+        dv.index_add_(2, ws + u, p.unsqueeze(-1) * d_o)
+    return dq, dk, dv
+
+
+# --------------------------------------------------------------------------- unfused pair
+def natten2d_qk(q, k, kernel_size: int, acc_dtype=torch.float64):
+    """Window scores (B, N, H, W, ks*ks): member j = (row j // ks, column j % ks) of the clamped
+    window.  Differentiable."""
+    B, N, H, W, C = q.shape
+    ks = kernel_size
+    q, k = q.to(acc_dtype), k.to(acc_dtype)
+    wsx, wsy = window_start_table(H, ks), window_start_table(W, ks)
+    return torch.stack([(q * _shifted(k, wsx, wsy, u, w)).sum(-1) for u in range(ks) for w in range(ks)], dim=-1)
+
+
+def natten2d_av(attn, v, kernel_size: int, acc_dtype=torch.float64):
+    """Applies window weights (B, N, H, W, ks*ks) to the values.  Differentiable."""
+    B, N, H, W, C = v.shape
+    ks = kernel_size
+    attn, v = attn.to(acc_dtype), v.to(acc_dtype)
+    wsx, wsy = window_start_table(H, ks), window_start_table(W, ks)
+    return sum(attn[..., u * ks + w].unsqueeze(-1) * _shifted(v, wsx, wsy, u, w) for u in range(ks) for w in range(ks))
 
 
 def round_inputs(shape, dtype, seed: int, scale: float = 1.0, q_scale: float = 1.0):

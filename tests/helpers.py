@@ -13,7 +13,8 @@ TOL = {
 
 
 def assert_close(got, want, dtype, what=""):
-    """|got - want| <= atol + rtol*|want| (+ rms_rel*rms(want) on the fp32 path), in fp64."""
+    """fp32 path: |got - want| <= rtol * max(|want|, rms(want)); 16-bit paths:
+    |got - want| <= atol + rtol*|want|.  Compared in fp64."""
     tol = TOL[dtype]
     got = got.detach().to("cpu", torch.float64)
     want = want.detach().to("cpu", torch.float64)
@@ -21,7 +22,10 @@ def assert_close(got, want, dtype, what=""):
     assert torch.isfinite(got).all(), f"{what}: non-finite values"
     err = (got - want).abs()
     rms = want.pow(2).mean().sqrt().item() if want.numel() else 0.0
-    bound = tol["atol"] + tol["rtol"] * want.abs() + tol["rms_rel"] * rms
+    if tol["rms_rel"] > 0.0:
+        bound = tol["atol"] + torch.maximum(tol["rtol"] * want.abs(), torch.full_like(want, tol["rms_rel"] * rms))
+    else:
+        bound = tol["atol"] + tol["rtol"] * want.abs()
     bad = err > bound
     if bad.any():
         idx = torch.nonzero(bad)[0].tolist()

@@ -18,7 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _declared_functions():
     text = open(os.path.join(ROOT, "include", "na2d.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(na2d_[a-z_0-9]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(na[12]d_[a-z_0-9]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_version_and_strerror():
-    assert _lib.lib.na2d_version() >= 100
+    assert _lib.lib.na2d_version() >= 200
     for code in range(0, -8, -1):
         assert len(_lib.lib.na2d_strerror(code)) > 0
 
@@ -71,6 +71,61 @@ def test_forward_refuses_bad_arguments_without_touching_cuda():
     assert _fwd(rows=C.byref(_lib.Rows(8, 8, 6, 9, 32))) == _lib.ERR_WINDOW
     assert _fwd(rows=C.byref(_lib.Rows(30, 8, 20, 12, 32))) == _lib.ERR_BAD_ARG
     assert _fwd(rows=C.byref(ok)) in (_lib.ERR_CUDA, _lib.ERR_NO_DEVICE)     # past validation: needs a GPU
+
+
+def _args(**kw):
+    a = _lib.Args()
+    a.struct_size = C.sizeof(_lib.Args)
+    a.op, a.B, a.N, a.H, a.W, a.C, a.kernel_size, a.dtype, a.path, a.device = 0, 1, 1, 8, 8, 32, 5, 1, 0, 0
+    a.scale = 1.0
+    for name in ("q", "k", "v", "o"):
+        setattr(a, name, _lib.TensorDesc(256, 0, 0, 0, 0))       # dummy, never dereferenced
+    a.lse = 256
+    for k_, v_ in kw.items():
+        setattr(a, k_, v_)
+    return a
+
+
+def test_ex_entry_points_refuse_bad_arguments_without_touching_cuda():
+    fwd = lambda a: _lib.lib.na2d_forward_ex(C.byref(a))
+    assert _lib.lib.na2d_forward_ex(None) == _lib.ERR_BAD_ARG
+    assert fwd(_args(struct_size=8)) == _lib.ERR_BAD_ARG            # a caller built against another header
+    assert fwd(_args(scale=0.0)) == _lib.ERR_BAD_ARG
+    assert fwd(_args(scale=-1.0)) == _lib.ERR_BAD_ARG
+    assert fwd(_args(scale=float("nan"))) == _lib.ERR_BAD_ARG
+    assert fwd(_args(op=7)) == _lib.ERR_BAD_ARG
+    assert fwd(_args(op=_lib.OP_1D)) == _lib.ERR_BAD_ARG            # the 1D operator wants H = 1
+    assert fwd(_args(op=_lib.OP_1D, H=1, W=4)) == _lib.ERR_WINDOW   # sequence shorter than the window
+    assert fwd(_args(kernel_size=6)) == _lib.ERR_BAD_ARG
+    # a layout the tensor-core kernels cannot take (TMA wants 16-byte multiples): refused when that
+    # path is demanded, served by the SIMT kernels under AUTO (which then needs a GPU)
+    odd = _lib.TensorDesc(256, 8 * 8 * 36, 8 * 8 * 36, 8 * 36, 36)
+    assert fwd(_args(q=odd, path=_lib.PATH_TENSOR)) == _lib.ERR_UNSUPPORTED
+    assert fwd(_args(q=_lib.TensorDesc(258, 0, 0, 0, 0), path=_lib.PATH_TENSOR)) == _lib.ERR_UNSUPPORTED
+    assert fwd(_args(q=odd)) in (_lib.ERR_CUDA, _lib.ERR_NO_DEVICE)
+    assert fwd(_args()) in (_lib.ERR_CUDA, _lib.ERR_NO_DEVICE)      # past validation: needs a GPU
+
+
+def test_unfused_pair_and_1d_refuse_bad_arguments_without_touching_cuda():
+    p = C.c_void_p(256)
+    assert _lib.lib.na2d_qk_forward(None, p, p, 1, 1, 8, 8, 32, 5, 0, 0, None) == _lib.ERR_BAD_ARG
+    assert _lib.lib.na2d_qk_forward(p, p, p, 1, 1, 4, 8, 32, 5, 0, 0, None) == _lib.ERR_WINDOW
+    assert _lib.lib.na2d_av_forward(p, p, p, 1, 1, 8, 8, 32, 4, 0, 0, None) == _lib.ERR_BAD_ARG
+    assert _lib.lib.na2d_av_backward(p, p, p, p, None, 1, 1, 8, 8, 32, 5, 0, 0, None) == _lib.ERR_BAD_ARG
+    assert _lib.lib.na1d_forward(p, p, p, p, p, 1, 1, 4, 32, 5, 0, 0, None) == _lib.ERR_WINDOW
+    assert _lib.lib.na1d_forward(p, p, p, p, None, 1, 1, 16, 32, 5, 0, 0, None) == _lib.ERR_BAD_ARG
+
+
+def test_kernel_ready_layouts():
+    """Which tensors go to the kernels in place and which are copied first."""
+    from e_natten_b200.functional import _kernel_ready
+    packed = torch.zeros(2, 10, 9, 3, 4, 64, dtype=torch.bfloat16)          # (B, H, W, 3, heads, C)
+    q = packed[:, :, :, 0].permute(0, 3, 1, 2, 4)
+    assert not q.is_contiguous() and _kernel_ready(q)
+    assert not _kernel_ready(packed[:, :, :, 0].permute(0, 3, 1, 4, 2))     # channels not contiguous
+    assert not _kernel_ready(torch.zeros(1, 1, 8, 8, 36, dtype=torch.bfloat16)[..., :32][:, :, :, 1:])  # stride 36
+    assert _kernel_ready(torch.zeros(1, 1, 8, 8, 36)[..., :32])             # fp32: any strides
+    assert not _kernel_ready(torch.zeros(1, 1, 8, 1, 32).expand(1, 1, 8, 8, 32))
 
 
 def test_python_wrapper_refuses_cpu_tensors_and_bad_shapes():

@@ -13,18 +13,21 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def run_gpu(q, k, v, d_o, ks, path="auto", rows=None):
-    """(o, lse, dq, dk, dv) from the library's raw entry points."""
+def run_gpu(q, k, v, d_o, ks, path="auto", rows=None, with_o=True, scale=1.0):
+    """(o, lse, dq, dk, dv) from the library's raw entry points.  `with_o`: hand the forward's
+    output to the backward (what the autograd entry point does; the dQ kernel of the larger
+    windows then takes its one-walk form); False runs the backward without it (two walks)."""
     qd, kd, vd, gd = (t.to(DEV) for t in (q, k, v, d_o))
-    o, lse = na.natten2d_forward(qd, kd, vd, ks, rows=rows, path=path)
-    dq, dk, dv = na.natten2d_backward(qd, kd, vd, o, lse, gd, ks, rows=rows, path=path)
+    o, lse = na.natten2d_forward(qd, kd, vd, ks, rows=rows, path=path, scale=scale)
+    dq, dk, dv = na.natten2d_backward(qd, kd, vd, o if with_o else None, lse, gd, ks, rows=rows, path=path,
+                                      scale=scale)
     na.check_kernels(DEV)
     return o, lse, dq, dk, dv
 
 
-def check_against_oracle(shape, ks, dtype, seed, path="auto", scale=1.0, q_scale=1.0):
+def check_against_oracle(shape, ks, dtype, seed, path="auto", scale=1.0, q_scale=1.0, with_o=True):
     q, k, v, d_o = make_inputs(shape, dtype, seed, scale, q_scale)
-    o, lse, dq, dk, dv = run_gpu(q, k, v, d_o, ks, path)
+    o, lse, dq, dk, dv = run_gpu(q, k, v, d_o, ks, path, with_o=with_o)
     ro, rlse, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks)
     tag = f"{tuple(shape)} ks={ks} {dtype} {path}"
     assert_close(o, ro, dtype, f"o {tag}")
@@ -133,6 +136,34 @@ def test_default_path_unscaled_logits_fp16(shape, ks):
     check_against_oracle(shape, ks, torch.float16, seed=300 + ks, path="auto")
 
 
+# ------------------------------------------------------------------------------ every tensor-core instantiation
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("ks", [3, 5, 7, 9, 11, 13])
+@pytest.mark.parametrize("D", [32, 64, 128])
+def test_every_tensor_core_instantiation(D, ks, dtype):
+    """Each (head dim, kernel size, dtype) triple is a kernel family of its own (chunking, shared
+    and tensor memory plan, mask constants): forward, dQ and dK/dV of every one of them against
+    the oracle on a ragged grid, with and without the forward's output handed to the backward
+    (kernel sizes >= 7: the one-walk and the two-walk form of the dQ kernel), and the row deltas
+    of the full and of the delta-only call."""
+    shape = (1, 2, ks + 10, ks + 13, D)
+    seed = 1000 + 100 * ks + D
+    check_against_oracle(shape, ks, dtype, seed, path="tensor", q_scale=D ** -0.5)
+    if ks >= 7:
+        check_against_oracle(shape, ks, dtype, seed, path="tensor", q_scale=D ** -0.5, with_o=False)
+        check_against_oracle(shape, ks, dtype, seed + 1, path="tensor")     # unscaled logits, near one-hot rows
+    q, k, v, d_o = make_inputs(shape, dtype, seed, q_scale=D ** -0.5)
+    qd, kd, vd, gd = (t.to(DEV) for t in (q, k, v, d_o))
+    o, lse = na.natten2d_forward(qd, kd, vd, ks, path="tensor")
+    ro, _, _, _, _ = orc.natten2d_fwd_bwd(q, k, v, d_o, ks)
+    want = (d_o.double() * ro).sum(-1)
+    for dq_buf in (None, torch.empty_like(qd)):
+        delta = torch.full_like(lse, float("nan"))
+        na.functional.backward_dq_into(qd, kd, vd, o, lse, gd, dq_buf, delta, ks, path="tensor")
+        na.check_kernels(DEV)
+        assert_close(delta, want, dtype, f"delta D={D} ks={ks} dQ={'yes' if dq_buf is not None else 'no'}")
+
+
 # ------------------------------------------------------------------------------ BASELINE configs
 def test_config1_fp32():
     check_against_oracle((1, 2, 16, 16, 32), 5, torch.float32, seed=0)
@@ -180,11 +211,12 @@ def _band_check(q, k, v, d_o, got, ks, bn_list, bands, dtype):
                 assert_close(sl(dv, r0, r1), rdv[:, :, r0 - kv0:r1 - kv0], dtype, "dv " + tag)
 
 
-@pytest.mark.parametrize("side", [128, 192, 256])
-def test_config2_large_sides_bands_and_cross_path(side):
+@pytest.mark.parametrize("side,dtype", [(128, torch.bfloat16), (192, torch.bfloat16), (256, torch.bfloat16),
+                                        (128, torch.float16), (256, torch.float16)])
+def test_config2_large_sides_bands_and_cross_path(side, dtype):
     """Sides the CPU oracle cannot finish whole: oracle on border / interior row bands of two
     units, plus the two GPU paths against each other on the full tensors."""
-    dtype, ks = torch.bfloat16, 5
+    ks = 5
     q, k, v, d_o = make_inputs((4, 4, side, side, 128), dtype, 0, q_scale=128 ** -0.5)
     got = run_gpu(q, k, v, d_o, ks, "auto")
     bands = [(0, 12), (side // 2 - 6, side // 2 + 6), (side - 12, side)]
@@ -196,22 +228,33 @@ def test_config2_large_sides_bands_and_cross_path(side):
 
 def test_config5_huge_image_bands():
     """B1 N8 1024x1024 C128 ks13 bf16 seed 3, whole image on one GPU: oracle on the top border,
-    the bottom border, every 8-way shard boundary +-(ks-1) rows of one head, and one interior
-    band of another head."""
+    the bottom border and all seven 8-way shard boundaries +-(ks-1) rows (all columns are kept,
+    because a narrower problem would change the clamping; the nine bands are spread over the
+    heads, one head each), one interior band of another head, and the SIMT kernels against the
+    tensor-core kernels on the whole of one head."""
     dtype, ks, S = torch.bfloat16, 13, 1024
     q, k, v, d_o = make_inputs((1, 8, S, S, 128), dtype, 3)
     got = run_gpu(q, k, v, d_o, ks, "auto")
     bands = [(0, 16), (S - 16, S)] + [(r - 12, r + 12) for r in range(128, S, 128)]
-    # limit the oracle's work: a 64-column-wide problem would change clamping, so all columns
-    # are kept but only one head is checked at every band
-    _band_check(q, k, v, d_o, got, ks, [(0, 5)], bands[:4], dtype)
+    assert len(bands) == 9
+    for i, band in enumerate(bands):
+        _band_check(q, k, v, d_o, got, ks, [(0, i % 8)], [band], dtype)
     _band_check(q, k, v, d_o, got, ks, [(0, 2)], [(500, 520)], dtype)
+    head = 6
+    one = [t[:, head:head + 1] for t in (q, k, v, d_o)]
+    ref = run_gpu(*one, ks, "simt")
+    for name, a, b in zip(("o", "lse", "dq", "dk", "dv"), got, ref):
+        assert_close(a[:, head:head + 1], b.double(), dtype, f"{name} auto vs simt, config 5 head {head}")
 
 
 # ------------------------------------------------------------------------------ row views
-@pytest.mark.parametrize("dtype,path", [(torch.float32, "simt"), (torch.bfloat16, "auto")])
-def test_row_bands_reassemble_whole_image(dtype, path):
-    ks, H, W = 7, 45, 24
+@pytest.mark.parametrize("dtype,path,ks", [(torch.float32, "simt", 7), (torch.bfloat16, "auto", 7),
+                                           (torch.bfloat16, "auto", 3), (torch.bfloat16, "auto", 5),
+                                           (torch.float16, "auto", 5), (torch.bfloat16, "auto", 13)])
+def test_row_bands_reassemble_whole_image(dtype, path, ks):
+    """Every kernel family under a row view with non-zero first rows: the strip kernels of kernel
+    sizes 3 and 5, the chunked kernels of the larger windows, and the SIMT kernels."""
+    H, W = 45, 24
     q, k, v, d_o = make_inputs((2, 2, H, W, 64), dtype, 9)
     o, lse, dq, dk, dv = run_gpu(q, k, v, d_o, ks, path)
     dk_sum = torch.zeros_like(dk, dtype=torch.float32)
@@ -383,3 +426,127 @@ def test_errors_are_python_exceptions():
         na.natten2d_forward(q, q, q, 3, path="tensor")            # fp32 has no tensor-core path
     empty = torch.zeros(0, 1, 8, 8, 32, device=DEV)
     assert na.natten2d(empty, empty, empty, 3).shape == empty.shape
+
+
+# ------------------------------------------------------------------------------ scale and strided layouts
+@pytest.mark.parametrize("dtype,shape,ks,path", [(torch.float32, (1, 2, 12, 13, 32), 5, "auto"),
+                                                 (torch.bfloat16, (2, 2, 20, 24, 64), 5, "tensor"),
+                                                 (torch.bfloat16, (1, 2, 22, 24, 128), 7, "tensor"),
+                                                 (torch.float16, (1, 2, 20, 28, 32), 13, "tensor"),
+                                                 (torch.bfloat16, (1, 2, 20, 24, 64), 9, "simt")])
+def test_softmax_scale_argument(dtype, shape, ks, path):
+    """The scale argument of the kernels against the oracle (which scales q); unscaled N(0,1)
+    inputs, scale = head_dim**-0.5 as a caller of the reference would apply to q."""
+    scale = shape[-1] ** -0.5
+    q, k, v, d_o = make_inputs(shape, dtype, 77)
+    o, lse, dq, dk, dv = run_gpu(q, k, v, d_o, ks, path, scale=scale)
+    ro, rlse, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks, scale=scale)
+    tag = f"{shape} ks={ks} {dtype} {path} scale"
+    for name, a, b in (("o", o, ro), ("lse", lse, rlse), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        assert_close(a, b, dtype, f"{name} {tag}")
+    # and through the autograd entry point
+    qd, kd, vd = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    na.natten2d(qd, kd, vd, ks, scale).backward(d_o.to(DEV))
+    if path == "auto" or (path == "tensor" and dtype != torch.float32):
+        assert_close(qd.grad, rdq, dtype, "dq through natten2d(scale=...)")
+
+
+@pytest.mark.parametrize("dtype,Cd,ks", [(torch.bfloat16, 64, 5), (torch.float16, 128, 7), (torch.float32, 32, 5)])
+def test_packed_qkv_views_run_without_copies(dtype, Cd, ks):
+    """q, k, v as views of one (B, H, W, 3, heads, C) projection output, the layout the reference
+    refuses (e_natten/triton.py:233-234): the kernels read them in place (tensor maps / pointer
+    arithmetic built from the views' strides) and write dQ, dK, dV straight into views of a packed
+    gradient buffer."""
+    B, H, W, N = 2, 20, 24, 2
+    g = torch.Generator().manual_seed(5)
+    packed = (torch.randn((B, H, W, 3, N, Cd), generator=g) * 0.5).to(dtype).to(DEV)
+    d_o = torch.randn((B, H, W, N, Cd), generator=g).to(dtype).to(DEV).permute(0, 3, 1, 2, 4)     # strided too
+    q, k, v = (packed[:, :, :, i].permute(0, 3, 1, 2, 4) for i in range(3))
+    assert not q.is_contiguous() and all(na.as_kernel_input(t) is t for t in (q, k, v, d_o))
+    before = na.launch_count()
+    o, lse = na.natten2d_forward(q, k, v, ks)
+    d_packed = torch.full_like(packed, float("nan"))
+    dq, dk, dv = (d_packed[:, :, :, i].permute(0, 3, 1, 2, 4) for i in range(3))
+    delta = torch.empty_like(lse)
+    na.functional.backward_dq_into(q, k, v, o, lse, d_o, dq, delta, ks)
+    na.functional.backward_dkdv_into(q, k, v, lse, d_o, delta, dk, dv, ks)
+    na.check_kernels(DEV)
+    # forward, dQ, dK/dV and nothing else (the tensor-core dQ of kernel sizes >= 7 is preceded by its delta estimate)
+    assert na.launch_count() - before == (4 if (ks >= 7 and dtype != torch.float32) else 3)
+    ro, rlse, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q.cpu(), k.cpu(), v.cpu(), d_o.cpu(), ks)
+    assert torch.isfinite(d_packed.float()).all()                            # every element of the packed gradient written
+    for name, a, b in (("o", o, ro), ("lse", lse, rlse), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        assert_close(a, b, dtype, f"{name} from packed qkv views, {dtype}")
+    # the autograd entry point takes the same views
+    pk = packed.clone().requires_grad_()
+    q2, k2, v2 = (pk[:, :, :, i].permute(0, 3, 1, 2, 4) for i in range(3))
+    na.natten2d(q2, k2, v2, ks).backward(d_o)
+    assert_close(pk.grad[:, :, :, 0].permute(0, 3, 1, 2, 4), rdq, dtype, "packed dq through autograd")
+    assert_close(pk.grad[:, :, :, 2].permute(0, 3, 1, 2, 4), rdv, dtype, "packed dv through autograd")
+
+
+def test_layouts_the_tensor_maps_cannot_take_are_copied():
+    """Channels not contiguous, or strides that are not multiples of 16 bytes: the wrapper makes a
+    dense copy and the result is unchanged."""
+    q, k, v, d_o = make_inputs((1, 2, 16, 18, 32), torch.bfloat16, 6, q_scale=32 ** -0.5)
+    wide = torch.zeros((1, 2, 16, 18, 36), dtype=torch.bfloat16, device=DEV)
+    wide[..., 2:34] = q.to(DEV)
+    qv = wide[..., 2:34]                                       # pixel stride 36 elements, base off by 4 bytes
+    assert na.as_kernel_input(qv) is not qv
+    o1, _ = na.natten2d_forward(qv, k.to(DEV), v.to(DEV), 5)
+    o2, _ = na.natten2d_forward(q.to(DEV), k.to(DEV), v.to(DEV), 5)
+    assert torch.equal(o1, o2)
+
+
+# ------------------------------------------------------------------------------ bounded waits
+def test_bounded_wait_gives_up_and_is_reported_once():
+    """A wait that nothing ever satisfies ends by itself: the self-test kernel waits 2 ms on a
+    barrier nobody completes, records that, and exits normally.  na2d_check reports it once and
+    clears it; the next call is clean and the kernels still compute correctly afterwards."""
+    import ctypes as C
+    from e_natten_b200 import _lib
+    na.check_kernels(DEV)                                       # start clean
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(_lib.lib.na2d_selftest_wait_timeout(0, st, 2000))
+    assert _lib.lib.na2d_check(0, st) == _lib.ERR_KERNEL_WAIT
+    assert _lib.lib.na2d_check(0, st) == 0
+    with pytest.raises(ValueError):
+        _lib.check(_lib.lib.na2d_selftest_wait_timeout(0, st, 0))
+    check_against_oracle((1, 2, 17, 19, 64), 5, torch.bfloat16, seed=3, q_scale=0.125)
+
+
+def test_poll_reports_a_tripped_wait_without_synchronising():
+    """na2d_poll answers from the copy the previous poll started: clean, then (after the
+    self-test kernel) the error, then clean again.  The autograd backward polls at its entry and
+    raises there."""
+    import ctypes as C
+    from e_natten_b200 import _lib
+    na.check_kernels(DEV)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert _lib.lib.na2d_poll(0, st) == 0
+    torch.cuda.synchronize()
+    assert _lib.lib.na2d_poll(0, st) == 0                       # the first poll's copy saw a clean word
+    _lib.check(_lib.lib.na2d_selftest_wait_timeout(0, st, 1000))
+    assert _lib.lib.na2d_poll(0, st) == 0                       # asks; the answer comes with the next poll
+    torch.cuda.synchronize()
+    assert _lib.lib.na2d_poll(0, st) == _lib.ERR_KERNEL_WAIT
+    torch.cuda.synchronize()
+    _lib.lib.na2d_poll(0, st)                                   # (the copy enqueued before the clear may still see it)
+    torch.cuda.synchronize()
+    assert _lib.lib.na2d_poll(0, st) == 0
+    # through autograd: the error of an earlier kernel surfaces at the next backward's entry
+    q, k, v, d_o = (t.to(DEV) for t in make_inputs((1, 1, 12, 12, 32), torch.bfloat16, 2))
+    qg = q.clone().requires_grad_()
+    o = na.natten2d(qg, k, v, 5)
+    _lib.check(_lib.lib.na2d_selftest_wait_timeout(0, st, 1000))
+    na.poll_kernels(DEV)                                        # asks
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        o.backward(d_o)
+    torch.cuda.synchronize()
+    na.check_kernels(DEV) if False else None
+    _lib.lib.na2d_check(0, st)                                  # leave the word clean for the tests that follow
+    torch.cuda.synchronize()
+    _lib.lib.na2d_poll(0, st)
+    torch.cuda.synchronize()
+    _lib.lib.na2d_poll(0, st)

@@ -67,7 +67,9 @@ def _worker(rank, world, port, shape, ks, dtype, result):
 
 
 @pytest.mark.parametrize("shape,ks,dtype", [((1, 2, 64, 40, 64), 7, torch.bfloat16),
-                                            ((1, 2, 48, 24, 128), 13, torch.float16)])
+                                            ((1, 2, 48, 24, 128), 13, torch.float16),
+                                            ((2, 2, 40, 24, 128), 5, torch.bfloat16),     # strip kernels
+                                            ((1, 2, 36, 40, 64), 3, torch.float16)])
 def test_row_sharded_two_gpus(shape, ks, dtype):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
