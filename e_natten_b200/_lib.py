@@ -36,13 +36,14 @@ class Args(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("op", C.c_int),
                 ("B", C.c_int), ("N", C.c_int), ("H", C.c_int), ("W", C.c_int), ("C", C.c_int),
                 ("kernel_size", C.c_int), ("dtype", C.c_int), ("path", C.c_int), ("device", C.c_int),
-                ("scale", C.c_float), ("stream", C.c_void_p), ("rows", C.POINTER(Rows)),
+                ("flags", C.c_int), ("scale", C.c_float), ("stream", C.c_void_p), ("rows", C.POINTER(Rows)),
                 ("q", TensorDesc), ("k", TensorDesc), ("v", TensorDesc), ("o", TensorDesc),
                 ("d_o", TensorDesc), ("d_q", TensorDesc), ("d_k", TensorDesc), ("d_v", TensorDesc),
                 ("lse", C.c_void_p), ("delta", C.c_void_p)]
 
 
 OP_2D, OP_1D = 0, 1
+FLAG_DKDV_F32 = 1
 _DENSE = [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]      # B..dtype, rows, path, device, stream
 _PAIR = [C.c_int] * 7 + [C.c_int, C.c_void_p]                                  # B..dtype, device, stream
 

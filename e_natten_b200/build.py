@@ -52,10 +52,10 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > built for d in _deps())
 
 
-def _compile(unit, verbose: bool, extra):
+def _compile(unit, verbose: bool, extra, obj_dir):
     src, defines, obj = unit
     cmd = [_nvcc(), *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), *defines, "-c",
-           os.path.join(CSRC, src), "-o", os.path.join(OBJ_DIR, obj)]
+           os.path.join(CSRC, src), "-o", os.path.join(obj_dir, obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     return obj, proc.returncode, proc.stdout + proc.stderr, " ".join(cmd)
 
@@ -64,17 +64,19 @@ def build(force: bool = False, verbose: bool = False, extra_flags=(), lib_path: 
     """Compile the library if it is missing or older than its sources; return its path."""
     if not force and lib_path == LIB_PATH and not _stale():
         return LIB_PATH
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    # a library built elsewhere with other flags (a development build) keeps its objects apart
+    obj_dir = OBJ_DIR if lib_path == LIB_PATH else lib_path + ".objs"
+    os.makedirs(obj_dir, exist_ok=True)
     workers = max(1, min(len(UNITS), os.cpu_count() or 1))
     with concurrent.futures.ThreadPoolExecutor(workers) as pool:
-        results = list(pool.map(lambda u: _compile(u, verbose, list(extra_flags)), UNITS))
+        results = list(pool.map(lambda u: _compile(u, verbose, list(extra_flags), obj_dir), UNITS))
     for obj, rc, out, cmd in results:
         if verbose or rc != 0:
             sys.stderr.write(f"--- {obj}\n{out}")
         if rc != 0:
             raise RuntimeError("nvcc failed building %s (command: %s)" % (obj, cmd))
     link = [_nvcc(), "-shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a",
-            *[os.path.join(OBJ_DIR, u[2]) for u in UNITS], "-o", lib_path]
+            *[os.path.join(obj_dir, u[2]) for u in UNITS], "-o", lib_path]
     proc = subprocess.run(link, capture_output=True, text=True)
     if proc.returncode != 0:
         sys.stderr.write(proc.stdout + proc.stderr)

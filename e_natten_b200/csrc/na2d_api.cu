@@ -121,6 +121,7 @@ struct Problem {
     int B = 0;
     int dtype = 0;
     bool tensor = false;      // run the tcgen05 kernels
+    bool dkdv_f32 = false;    // dK / dV are fp32 tensors
     int device = 0;
     cudaStream_t st = nullptr;
     Tensor q, k, v, o, d_o, d_q, d_k, d_v;
@@ -217,6 +218,8 @@ int make_problem(const na2d_args* a, Problem* out) {
     p.g = g; p.B = B; p.dtype = dtype; p.tensor = tensor;
     p.device = a->device; p.st = (cudaStream_t)a->stream;
     p.lse = a->lse; p.delta = a->delta;
+    p.dkdv_f32 = (a->flags & NA2D_FLAG_DKDV_F32) != 0 && dtype != NA2D_F32;
+    if (a->flags & ~NA2D_FLAG_DKDV_F32) return NA2D_ERR_BAD_ARG;
     return NA2D_OK;
 }
 
@@ -262,7 +265,7 @@ int launch_ctx(const Problem& p, int* launched, na2d_tc::LaunchCtx* lc) {
     unsigned int* err = nullptr;
     int rc = error_word_address(p.device, &err);
     if (rc != NA2D_OK) return rc;
-    *lc = na2d_tc::LaunchCtx{p.g, p.dtype, p.B, p.device, p.st, err, launched};
+    *lc = na2d_tc::LaunchCtx{p.g, p.dtype, p.B, p.device, p.st, err, launched, p.dkdv_f32};
     return NA2D_OK;
 }
 
@@ -360,7 +363,7 @@ int run_backward_dkdv(const Problem& p) {
         using T = typename decltype(tt)::type;
         na2d_simt::dkdv_kernel<T, decltype(cpl)::value><<<grid, kSimtThreads, 0, p.st>>>(
             (const T*)p.q.ptr, (const T*)p.k.ptr, (const T*)p.v.ptr, p.lse, (const T*)p.d_o.ptr, p.delta,
-            (T*)p.d_k.ptr, (T*)p.d_v.ptr, p.q.st, p.k.st, p.v.st, p.d_o.st, p.d_k.st, p.d_v.st, g);
+            p.d_k.ptr, p.d_v.ptr, p.dkdv_f32 ? 1 : 0, p.q.st, p.k.st, p.v.st, p.d_o.st, p.d_k.st, p.d_v.st, g);
         return after_launch();
     });
 }
@@ -754,20 +757,5 @@ int na2d_selftest_wait_timeout(int device, void* stream, unsigned int limit_us) 
 }
 
 long long na2d_launch_count(void) { return g_launches.load(); }
-
-#ifdef NA2D_TRACE
-// Development aid: copies the trace of CTA 0 of the last kernels to the host and clears it.
-int na2d_debug_trace(unsigned long long* out, int max_entries) {
-    unsigned int n = 0;
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(&n, na2d_tc::g_trace_n, sizeof(n));
-    if ((int)n > max_entries) n = max_entries;
-    if (n > 8192) n = 8192;
-    cudaMemcpyFromSymbol(out, na2d_tc::g_trace, n * sizeof(unsigned long long));
-    void* arr = nullptr;
-    if (cudaGetSymbolAddress(&arr, na2d_tc::g_trace) == cudaSuccess) cudaMemset(arr, 0, sizeof(na2d_tc::g_trace));
-    return (int)n;
-}
-#endif
 
 }  // extern "C"

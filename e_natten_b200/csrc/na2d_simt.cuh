@@ -299,9 +299,9 @@ __device__ __forceinline__ Inverse inverse_neighbourhood(int key_row_global, int
 template <typename T, int CPL>
 __global__ void __launch_bounds__(kWarps * 32)
 dkdv_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const float* __restrict__ lse,
-            const T* __restrict__ d_o, const float* __restrict__ delta, T* __restrict__ d_k, T* __restrict__ d_v,
-            const Na2dStride sq, const Na2dStride sk, const Na2dStride sv, const Na2dStride sg, const Na2dStride sdk,
-            const Na2dStride sdv, const Na2dGeom g) {
+            const T* __restrict__ d_o, const float* __restrict__ delta, void* __restrict__ d_k, void* __restrict__ d_v,
+            const int f32_out, const Na2dStride sq, const Na2dStride sk, const Na2dStride sv, const Na2dStride sg,
+            const Na2dStride sdk, const Na2dStride sdv, const Na2dGeom g) {
     __shared__ float s_p[kWarps][32], s_ds[kWarps][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = warp; t < kPatch; t += kWarps) {
@@ -351,8 +351,13 @@ dkdv_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restric
         }
         __syncwarp();
     }
-    store_row<T, CPL>(d_k + offset_of(sdk, px.b, px.n, px.h, px.w), acc_k, 1.f, g.C, lane);
-    store_row<T, CPL>(d_v + offset_of(sdv, px.b, px.n, px.h, px.w), acc_v, 1.f, g.C, lane);
+    if (f32_out) {          // partial sums of a row band, kept in fp32 for their owner to add up
+        store_row<float, CPL>(static_cast<float*>(d_k) + offset_of(sdk, px.b, px.n, px.h, px.w), acc_k, 1.f, g.C, lane);
+        store_row<float, CPL>(static_cast<float*>(d_v) + offset_of(sdv, px.b, px.n, px.h, px.w), acc_v, 1.f, g.C, lane);
+    } else {
+        store_row<T, CPL>(static_cast<T*>(d_k) + offset_of(sdk, px.b, px.n, px.h, px.w), acc_k, 1.f, g.C, lane);
+        store_row<T, CPL>(static_cast<T*>(d_v) + offset_of(sdv, px.b, px.n, px.h, px.w), acc_v, 1.f, g.C, lane);
+    }
     }
 }
 

@@ -197,6 +197,32 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint8_t*
     }
 }
 
+// The same with fp32 output (the partial dK / dV of a row band, which its owner adds to its own):
+// rounds of 16 channels, again 64-byte rows in the 64-byte swizzle of an fp32 tensor map whose box
+// is 16 channels wide.
+template <int NCOL>
+__device__ __forceinline__ void stage_and_store_f32(const CUtensorMap* map, uint8_t* stage, const uint32_t (&v)[NCOL],
+                                                    int ch0, int w0, int h0, int n, int b, int lane) {
+    static_assert(NCOL % 16 == 0, "rounds of 16 channels");
+    const uint32_t row = smem_u32(stage) + lane * 64;
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int r = 0; r < NCOL / 16; ++r) {
+        if (lane == 0) bulk_wait_read<0>();             // the previous store has read the buffer
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            st_shared_v4(row + ((c ^ sw) << 4), v[16 * r + 4 * c], v[16 * r + 4 * c + 1], v[16 * r + 4 * c + 2],
+                         v[16 * r + 4 * c + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_5d(map, smem_u32(stage), ch0 + 16 * r, w0, h0, n, b);
+            bulk_commit();
+        }
+    }
+}
+
 // Writes 16 consecutive 16-bit values (packed in pairs) of row `row` of the same operand layout,
 // at columns [16*block16, 16*block16 + 16).
 __device__ __forceinline__ void store_operand_block16(uint32_t base, int slab_bytes, int row, int block16,
@@ -251,17 +277,18 @@ struct TensorArg {
     Na2dStride st;
 };
 
-// Tensor map over a (B, N, rows, W, C) tensor of 16-bit elements with the caller's strides
-// (channels contiguous); coordinates are (channel, column, row, head, batch).  The box is
-// box_c channels (0: min(C, 64)) x box_w x box_h x 1 x 1, swizzled so that one box row is one
-// swizzle span.  Encoded maps are kept in a small per-thread cache: a training loop calls with the
-// same buffers step after step, and the driver call is a visible part of a small launch.
+// Tensor map over a (B, N, rows, W, C) tensor of 16-bit elements (fp32 when `f32`: an output map)
+// with the caller's strides (channels contiguous); coordinates are (channel, column, row, head,
+// batch).  The box is box_c channels (0: min(C, 64)) x box_w x box_h x 1 x 1, swizzled so that one
+// box row is one swizzle span.  Encoded maps are kept in a small per-thread cache: a training loop
+// calls with the same buffers step after step, and the driver call is a visible part of a small
+// launch.
 inline int make_map(CUtensorMap* map, const TensorArg& t, int dtype, int B, int N, int rows, int W, int C,
-                    int box_w, int box_h, int box_c = 0) {
+                    int box_w, int box_h, int box_c = 0, bool f32 = false) {
     struct Key {
         const void* ptr;
         long long sb, sn, sh, sw;
-        int dtype, B, N, rows, W, C, box_w, box_h, box_c, pad;
+        int dtype, B, N, rows, W, C, box_w, box_h, box_c, f32;
     };
     struct Entry {
         Key key;
@@ -275,7 +302,7 @@ inline int make_map(CUtensorMap* map, const TensorArg& t, int dtype, int B, int 
     std::memset(&key, 0, sizeof(key));
     key.ptr = t.ptr; key.sb = t.st.b; key.sn = t.st.n; key.sh = t.st.h; key.sw = t.st.w;
     key.dtype = dtype; key.B = B; key.N = N; key.rows = rows; key.W = W; key.C = C;
-    key.box_w = box_w; key.box_h = box_h; key.box_c = box_c;
+    key.box_w = box_w; key.box_h = box_h; key.box_c = box_c; key.f32 = f32 ? 1 : 0;
     for (int i = 0; i < kEntries; ++i) {
         if (cache[i].used && std::memcmp(&cache[i].key, &key, sizeof(Key)) == 0) {
             *map = cache[i].map;
@@ -286,13 +313,16 @@ inline int make_map(CUtensorMap* map, const TensorArg& t, int dtype, int B, int 
     if (!fn) return NA2D_ERR_CUDA;
     const int slab_c = box_c > 0 ? box_c : (C < 64 ? C : 64);
     cuuint64_t dims[5] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)rows, (cuuint64_t)N, (cuuint64_t)B};
-    cuuint64_t strides[4] = {(cuuint64_t)t.st.w * 2, (cuuint64_t)t.st.h * 2, (cuuint64_t)t.st.n * 2,
-                             (cuuint64_t)t.st.b * 2};
+    const cuuint64_t eb = f32 ? 4 : 2;
+    cuuint64_t strides[4] = {(cuuint64_t)t.st.w * eb, (cuuint64_t)t.st.h * eb, (cuuint64_t)t.st.n * eb,
+                             (cuuint64_t)t.st.b * eb};
     cuuint32_t box[5] = {(cuuint32_t)slab_c, (cuuint32_t)box_w, (cuuint32_t)box_h, 1, 1};
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    const CUtensorMapDataType dt = dtype == NA2D_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const CUtensorMapSwizzle sw = slab_c * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                  : (slab_c * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    const CUtensorMapDataType dt = f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                       : (dtype == NA2D_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    const int row_bytes = slab_c * (int)eb;
+    const CUtensorMapSwizzle sw = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     CUresult r = fn(map, dt, 5, const_cast<void*>(t.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -327,6 +357,7 @@ struct LaunchCtx {
     cudaStream_t st;
     unsigned int* err_word;
     int* launched;
+    bool dkdv_f32;         // the dK/dV kernel writes fp32 (partial sums of a row band)
 };
 
 // Register re-balancing of the 384-thread kernels (launched with 168 registers per thread): the
@@ -393,6 +424,16 @@ __device__ __forceinline__ void trace(int role, int ev, unsigned n) {
     g_trace[(role * 256 + n) * 8 + ev] = clock64();
 }
 #define NA2D_TR(role, ev, n) trace(role, ev, n)
+// Copies this translation unit's trace to the host and clears it (each unit has its own array).
+inline int copy_trace(unsigned long long* out, int max_entries) {
+    unsigned int n = 8192;
+    cudaDeviceSynchronize();
+    if ((int)n > max_entries) n = max_entries;
+    cudaMemcpyFromSymbol(out, g_trace, n * sizeof(unsigned long long));
+    void* arr = nullptr;
+    if (cudaGetSymbolAddress(&arr, g_trace) == cudaSuccess) cudaMemset(arr, 0, sizeof(g_trace));
+    return (int)n;
+}
 #else
 #define NA2D_TR(role, ev, n)
 #endif

@@ -23,3 +23,10 @@ int NA2D_TC_NAME(backward_dkdv)(const LaunchCtx& lc, const TensorArg& q, const T
 }
 
 }  // namespace na2d_tc
+
+#ifdef NA2D_TRACE
+// Development aid: the trace CTA 0 of this unit's kernels recorded (see na2d_tc.cuh).
+extern "C" int NA2D_TC_NAME(na2d_debug_trace_dkdv)(unsigned long long* out, int max_entries) {
+    return na2d_tc::copy_trace(out, max_entries);
+}
+#endif

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(512, 1)
 dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
             const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
             const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
-            const float* __restrict__ lse, const float* __restrict__ delta,
+            const float* __restrict__ lse, const float* __restrict__ delta, const int f32_out,
             unsigned int* __restrict__ err_word, const Na2dGeom g, const int tiles_r, const int tiles_c,
             const int total_tiles) {
     constexpr bool SPLIT = IsBf16<DT>::value;
@@ -318,9 +318,14 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
 #pragma unroll
                 for (int e = 0; e < 32; ++e) z[e] = 0u;
 #pragma unroll
-                for (int j = 0; j < 2 * RPO; ++j)
-                    stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
-                                            t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane);
+                for (int j = 0; j < 2 * RPO; ++j) {
+                    if (f32_out)
+                        stage_and_store_f32<32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 32 * (j % RPO), t.kc0,
+                                                t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane);
+                    else
+                        stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
+                                                t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane);
+                }
                 continue;
             }
             if (warp == 12 && lane == 0) NA2D_TR(0, 0, it);
@@ -343,8 +348,12 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     if (lane == 0) mbar_arrive(acc_free);
                     if (warp == 12 && lane == 0) NA2D_TR(0, 2, it);
                 }
-                stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 1.f, 32 * (j % RPO), t.kc0, h0,
-                                        t.hn, t.hb, lane);
+                if (f32_out)
+                    stage_and_store_f32<32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 32 * (j % RPO), t.kc0, h0,
+                                            t.hn, t.hb, lane);
+                else
+                    stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 1.f, 32 * (j % RPO), t.kc0, h0,
+                                            t.hn, t.hb, lane);
             }
             if (warp == 12 && lane == 0) NA2D_TR(0, 3, it);
             ++it;
@@ -508,8 +517,9 @@ int launch_dkdv(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, con
     const Na2dGeom& g = lc.g;
     CUtensorMap tk, tv, tq, tg, tdk, tdv;
     int rc = make_map(&tk, k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, TH);
-    if (rc == NA2D_OK) rc = make_map(&tdk, d_k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, 32 / TW, 32);
-    if (rc == NA2D_OK) rc = make_map(&tdv, d_v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, 32 / TW, 32);
+    const int out_c = lc.dkdv_f32 ? 16 : 32;
+    if (rc == NA2D_OK) rc = make_map(&tdk, d_k, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, 32 / TW, out_c, lc.dkdv_f32);
+    if (rc == NA2D_OK) rc = make_map(&tdv, d_v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, 32 / TW, out_c, lc.dkdv_f32);
     if (rc == NA2D_OK) rc = make_map(&tv, v, lc.dtype, lc.B, g.N, g.Hkv, g.W, D, TW, TH);
     if (rc == NA2D_OK) rc = make_map(&tq, q, lc.dtype, lc.B, g.N, g.Hq, g.W, D, C::HW, C::RC);
     if (rc == NA2D_OK) rc = make_map(&tg, d_o, lc.dtype, lc.B, g.N, g.Hq, g.W, D, C::HW, C::RC);
@@ -521,8 +531,8 @@ int launch_dkdv(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, con
     static std::atomic<unsigned long long> opted{0};
     if (opt_in_smem(kern, C::SMEM, lc.device, opted) != cudaSuccess) return NA2D_ERR_CUDA;
     const int grid = (int)(tiles < sm_count(lc.device) ? tiles : sm_count(lc.device));
-    kern<<<grid, 512, C::SMEM, lc.st>>>(tk, tv, tq, tg, tdk, tdv, lse, delta, lc.err_word, g, tiles_r, tiles_c,
-                                        (int)tiles);
+    kern<<<grid, 512, C::SMEM, lc.st>>>(tk, tv, tq, tg, tdk, tdv, lse, delta, lc.dkdv_f32 ? 1 : 0, lc.err_word, g,
+                                        tiles_r, tiles_c, (int)tiles);
     *lc.launched += 1;
     return cudaGetLastError() == cudaSuccess ? NA2D_OK : NA2D_ERR_CUDA;
 }

@@ -159,8 +159,13 @@ def backward_dq_into(q, k, v, o, lse, d_o, d_q, delta, kernel_size: int, rows=No
 
 def backward_dkdv_into(q, k, v, lse, d_o, delta, d_k, d_v, kernel_size: int, rows=None, path: str = "auto",
                        scale: float = 1.0) -> None:
-    """Launch the key half of the backward: reads ``delta``, writes ``d_k`` and ``d_v``."""
+    """Launch the key half of the backward: reads ``delta``, writes ``d_k`` and ``d_v``, which have
+    the inputs' dtype or, for 16-bit inputs, may both be fp32 (partial sums of a row band)."""
     a = _args(q, kernel_size, rows, path, scale, q=q, k=k, v=v, lse=lse, d_o=d_o, delta=delta, d_k=d_k, d_v=d_v)
+    if d_k.dtype != q.dtype:
+        if d_k.dtype != torch.float32 or d_v.dtype != torch.float32:
+            raise ValueError("d_k and d_v must have the inputs' dtype or both be float32")
+        a.flags |= _lib.FLAG_DKDV_F32
     _lib.check(_lib.lib.na2d_backward_dkdv_ex(C.byref(a)))
 
 
@@ -179,11 +184,12 @@ def natten2d_forward(q, k, v, kernel_size: int, rows: Optional[_lib.Rows] = None
 
 
 def natten2d_backward(q, k, v, o, lse, d_o, kernel_size: int, rows: Optional[_lib.Rows] = None,
-                      path: str = "auto", need_dq: bool = True, need_dkdv: bool = True, scale: float = 1.0):
+                      path: str = "auto", need_dq: bool = True, need_dkdv: bool = True, scale: float = 1.0,
+                      dkdv_dtype: Optional[torch.dtype] = None):
     """Raw backward: returns ``(dQ, dK, dV)`` (``None`` for a half that was not asked for).
 
     With a row view dK / dV have the key band's shape and hold the partial sums over the local
-    query band.
+    query band; ``dkdv_dtype=torch.float32`` keeps those partial sums in fp32.
     """
     _check_inputs(q, k, v, kernel_size, rows)
     q, k, v, d_o = (as_kernel_input(t) for t in (q, k, v, d_o))
@@ -193,8 +199,8 @@ def natten2d_backward(q, k, v, o, lse, d_o, kernel_size: int, rows: Optional[_li
         o = as_kernel_input(o)
     B, N, H, W, Cd = q.shape
     d_q = torch.empty(q.shape, dtype=q.dtype, device=q.device) if need_dq else None
-    d_k = torch.empty(k.shape, dtype=k.dtype, device=q.device) if need_dkdv else None
-    d_v = torch.empty(v.shape, dtype=v.dtype, device=q.device) if need_dkdv else None
+    d_k = torch.empty(k.shape, dtype=dkdv_dtype or k.dtype, device=q.device) if need_dkdv else None
+    d_v = torch.empty(v.shape, dtype=dkdv_dtype or v.dtype, device=q.device) if need_dkdv else None
     if q.numel() == 0 or not (need_dq or need_dkdv):
         return d_q, d_k, d_v
     delta = torch.empty((B, N, H, W), dtype=torch.float32, device=q.device)

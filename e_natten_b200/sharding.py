@@ -15,13 +15,27 @@ Two ways to split the work over the GPUs of one box, one process per GPU:
   rank's own memory before a kernel reads them.  The kernels clamp windows against the whole
   image through a row view (``na2d_rows``), so the result equals the single-GPU result.
 
+  How a step runs (``RowShardedNatten2d``):
+
+  - K and V live in *extended* buffers ``(B, N, top + R + bot, W, C)`` whose middle rows are the
+    rank's own; a caller that builds K / V directly in ``RowShardWorkspace.k_local`` / ``v_local``
+    pays no copy, any other K / V is copied into the middle once.
+  - The halo rows are received straight into the first / last rows of the extended buffers, one
+    contiguous run per (batch, head) slab, while the forward of the *interior* query rows - those
+    whose windows stay inside the rank's own rows - already runs; the two boundary strips of
+    ``kernel_size // 2`` query rows follow when the halo has arrived.
+  - The backward computes dQ for the band and the partial dK / dV for all extended rows in fp32
+    (a partial sum can be much larger than the total, so it is not rounded to 16 bits before it
+    is added), sends the halo rows' partials to their owners and adds what arrives for its own
+    edge rows; the sum is rounded once.
+
 The arithmetic is injected (``forward_fn`` / ``backward_fn``) so that the exchange logic can be
 exercised on CPU tensors in tests; by default it is the library's CUDA entry points.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Optional, Tuple
+from typing import Callable, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -62,8 +76,10 @@ class RowShard:
     def bot(self) -> int:          # halo rows owned by rank + 1
         return self.kv_row0 + self.Hkv - (self.row0 + self.R)
 
-    def rows(self):
-        return F.make_rows(self.row0, self.R, self.kv_row0, self.Hkv, self.H)
+    def rows(self, a: int = 0, b: Optional[int] = None):
+        """Row view of the local query rows [a, b) (default: the whole band) over the extended keys."""
+        b = self.R if b is None else b
+        return F.make_rows(self.row0 + a, b - a, self.kv_row0, self.Hkv, self.H)
 
 
 def plan_row_shard(H: int, world: int, rank: int, ks: int) -> RowShard:
@@ -77,78 +93,190 @@ def plan_row_shard(H: int, world: int, rank: int, ks: int) -> RowShard:
     return RowShard(rank, world, H, ks, first, count, kv0, kv1 - kv0)
 
 
-def _p2p(ops):
-    if ops:
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
+def _neighbours(shard: RowShard):
+    up = plan_row_shard(shard.H, shard.world, shard.rank - 1, shard.ks) if shard.rank > 0 else None
+    dn = plan_row_shard(shard.H, shard.world, shard.rank + 1, shard.ks) if shard.rank + 1 < shard.world else None
+    return up, dn
+
+
+def _peer(group, group_rank: int) -> int:
+    """The rank ``dist.P2POp`` wants: global, while a shard's rank counts inside ``group``."""
+    return group_rank if group is None else dist.get_global_rank(group, group_rank)
+
+
+def _partial_dtype(dtype: torch.dtype) -> torch.dtype:
+    """dtype in which partial dK / dV travel and are added."""
+    return torch.float32 if dtype in (torch.bfloat16, torch.float16) else dtype
+
+
+class RowShardWorkspace:
+    """The buffers of one rank that outlive a step: extended K / V (own rows in the middle, halo
+    rows around them), and the fp32 extended dK / dV with the receive buffers of their reduction.
+    ``k_local`` / ``v_local`` are views of the middle rows: K / V written there need no copy."""
+
+    def __init__(self, shard: RowShard, B: int, N: int, W: int, C: int, dtype: torch.dtype, device):
+        self.shard = shard
+        shape = (B, N, shard.Hkv, W, C)
+        self.k_ext = torch.empty(shape, dtype=dtype, device=device)
+        self.v_ext = torch.empty(shape, dtype=dtype, device=device)
+        self._partial = None
+        self._shape, self._dtype, self._device = shape, dtype, device
+
+    @property
+    def k_local(self) -> torch.Tensor:
+        return self.k_ext[:, :, self.shard.top:self.shard.top + self.shard.R]
+
+    @property
+    def v_local(self) -> torch.Tensor:
+        return self.v_ext[:, :, self.shard.top:self.shard.top + self.shard.R]
+
+    def matches(self, k: torch.Tensor) -> bool:
+        return tuple(k.shape) == tuple(self.k_local.shape) and k.dtype == self._dtype and k.device == self.k_ext.device
+
+    def partial_buffers(self):
+        """(dk_ext, dv_ext, recv_up, recv_dn): fp32 (or the inputs' wider dtype), allocated on first use."""
+        if self._partial is None:
+            sh = self.shard
+            B, N, _, W, C = self._shape
+            pd = _partial_dtype(self._dtype)
+            up, dn = _neighbours(sh)
+            mk = lambda rows: torch.empty((2, B, N, rows, W, C), dtype=pd, device=self._device) if rows > 0 else None
+            self._partial = (torch.empty(self._shape, dtype=pd, device=self._device),
+                             torch.empty(self._shape, dtype=pd, device=self._device),
+                             mk(up.bot if up is not None else 0), mk(dn.top if dn is not None else 0))
+        return self._partial
+
+
+def _slabs(t: torch.Tensor, rows: slice) -> List[torch.Tensor]:
+    """The contiguous per-(batch, head) runs of rows ``rows`` of a (B, N, rows, W, C) tensor."""
+    B, N = t.shape[:2]
+    return [t[b, n, rows] for b in range(B) for n in range(N)]
+
+
+def start_kv_halo_exchange(k_ext: torch.Tensor, v_ext: torch.Tensor, shard: RowShard, group=None):
+    """Starts the halo exchange of the extended K / V buffers (own rows already in the middle):
+    sends this rank's edge rows to the neighbours that see them and receives the halo rows straight
+    into the buffers' first / last rows.  Returns the pending requests; ``finish_exchange`` waits."""
+    up, dn = _neighbours(shard)
+    top, R = shard.top, shard.R
+    ops = []
+    for e in (k_ext, v_ext):
+        if up is not None:
+            if up.bot > 0:                                     # my first rows are rank-1's bottom halo
+                ops += [dist.P2POp(dist.isend, s, _peer(group, shard.rank - 1), group)
+                        for s in _slabs(e, slice(top, top + up.bot))]
+            if top > 0:
+                ops += [dist.P2POp(dist.irecv, s, _peer(group, shard.rank - 1), group) for s in _slabs(e, slice(0, top))]
+        if dn is not None:
+            if dn.top > 0:                                     # my last rows are rank+1's top halo
+                ops += [dist.P2POp(dist.isend, s, _peer(group, shard.rank + 1), group)
+                        for s in _slabs(e, slice(top + R - dn.top, top + R))]
+            if shard.bot > 0:
+                ops += [dist.P2POp(dist.irecv, s, _peer(group, shard.rank + 1), group)
+                        for s in _slabs(e, slice(top + R, shard.Hkv))]
+    return dist.batch_isend_irecv(ops) if ops else []
+
+
+def finish_exchange(reqs) -> None:
+    for req in reqs:
+        req.wait()
 
 
 def exchange_kv_halo(k_local: torch.Tensor, v_local: torch.Tensor, shard: RowShard,
                      group=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Returns K and V extended by the halo rows of the neighbouring bands:
-    shape (B, N, top + R + bot, W, C)."""
+    """Blocking form for callers without a workspace: returns K and V extended by the halo rows of
+    the neighbouring bands, shape (B, N, top + R + bot, W, C)."""
     B, N, R, W, C = k_local.shape
     assert R == shard.R
-    up = plan_row_shard(shard.H, shard.world, shard.rank - 1, shard.ks) if shard.rank > 0 else None
-    dn = plan_row_shard(shard.H, shard.world, shard.rank + 1, shard.ks) if shard.rank + 1 < shard.world else None
     ext = [t.new_empty((B, N, shard.Hkv, W, C)) for t in (k_local, v_local)]
     for e, t in zip(ext, (k_local, v_local)):
         e[:, :, shard.top:shard.top + R] = t
-    ops, staged = [], []
-    for e, t in zip(ext, (k_local, v_local)):
-        if up is not None:
-            if up.bot > 0:                                     # my first rows are rank-1's bottom halo
-                send = t[:, :, :up.bot].contiguous()
-                ops.append(dist.P2POp(dist.isend, send, shard.rank - 1, group))
-            if shard.top > 0:
-                recv = t.new_empty((B, N, shard.top, W, C))
-                ops.append(dist.P2POp(dist.irecv, recv, shard.rank - 1, group))
-                staged.append((e, slice(0, shard.top), recv))
-        if dn is not None:
-            if dn.top > 0:                                     # my last rows are rank+1's top halo
-                send = t[:, :, R - dn.top:].contiguous()
-                ops.append(dist.P2POp(dist.isend, send, shard.rank + 1, group))
-            if shard.bot > 0:
-                recv = t.new_empty((B, N, shard.bot, W, C))
-                ops.append(dist.P2POp(dist.irecv, recv, shard.rank + 1, group))
-                staged.append((e, slice(shard.top + R, shard.Hkv), recv))
-    _p2p(ops)
-    for e, sl, recv in staged:
-        e[:, :, sl] = recv
+    finish_exchange(start_kv_halo_exchange(ext[0], ext[1], shard, group))
     return ext[0], ext[1]
 
 
-def reduce_dkdv_halo(dk_ext: torch.Tensor, dv_ext: torch.Tensor, shard: RowShard,
-                     group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+def reduce_dkdv_halo(dk_ext: torch.Tensor, dv_ext: torch.Tensor, shard: RowShard, group=None,
+                     out_dtype: Optional[torch.dtype] = None, recv=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """The matching reduction of the backward: partial dK / dV computed here for the neighbours'
     rows go back to their owners; partials the neighbours computed for this band's edge rows are
-    added (in fp32, rounded once).  Returns dK, dV of shape (B, N, R, W, C)."""
+    added, in the partials' dtype (fp32 for 16-bit tensors), and the sum is rounded once to
+    ``out_dtype``.  Returns dK, dV of shape (B, N, R, W, C)."""
     B, N, Hkv, W, C = dk_ext.shape
-    R = shard.R
-    up = plan_row_shard(shard.H, shard.world, shard.rank - 1, shard.ks) if shard.rank > 0 else None
-    dn = plan_row_shard(shard.H, shard.world, shard.rank + 1, shard.ks) if shard.rank + 1 < shard.world else None
-    ops, adds = [], []
-    for e in (dk_ext, dv_ext):
+    R, top = shard.R, shard.top
+    up, dn = _neighbours(shard)
+    n_up = up.bot if up is not None else 0
+    n_dn = dn.top if dn is not None else 0
+    recv_up, recv_dn = recv if recv is not None else (None, None)
+    if n_up > 0 and recv_up is None:
+        recv_up = dk_ext.new_empty((2, B, N, n_up, W, C))
+    if n_dn > 0 and recv_dn is None:
+        recv_dn = dk_ext.new_empty((2, B, N, n_dn, W, C))
+    ops = []
+    for i, e in enumerate((dk_ext, dv_ext)):
         if up is not None:
-            if shard.top > 0:                                  # rows I computed that rank-1 owns
-                ops.append(dist.P2POp(dist.isend, e[:, :, :shard.top].contiguous(), shard.rank - 1, group))
-            if up.bot > 0:                                     # rank-1's partials for my first rows
-                recv = e.new_empty((B, N, up.bot, W, C))
-                ops.append(dist.P2POp(dist.irecv, recv, shard.rank - 1, group))
-                adds.append((e, slice(shard.top, shard.top + up.bot), recv))
+            if top > 0:                                        # rows I computed that rank-1 owns
+                ops += [dist.P2POp(dist.isend, s, _peer(group, shard.rank - 1), group) for s in _slabs(e, slice(0, top))]
+            if n_up > 0:                                       # rank-1's partials for my first rows
+                ops += [dist.P2POp(dist.irecv, s, _peer(group, shard.rank - 1), group)
+                        for s in _slabs(recv_up[i], slice(0, n_up))]
         if dn is not None:
             if shard.bot > 0:
-                ops.append(dist.P2POp(dist.isend, e[:, :, shard.top + R:].contiguous(), shard.rank + 1, group))
-            if dn.top > 0:
-                recv = e.new_empty((B, N, dn.top, W, C))
-                ops.append(dist.P2POp(dist.irecv, recv, shard.rank + 1, group))
-                adds.append((e, slice(shard.top + R - dn.top, shard.top + R), recv))
-    _p2p(ops)
-    for e, sl, recv in adds:
-        acc = torch.promote_types(e.dtype, torch.float32)
-        e[:, :, sl] = (e[:, :, sl].to(acc) + recv.to(acc)).to(e.dtype)
-    return (dk_ext[:, :, shard.top:shard.top + R].contiguous(),
-            dv_ext[:, :, shard.top:shard.top + R].contiguous())
+                ops += [dist.P2POp(dist.isend, s, _peer(group, shard.rank + 1), group)
+                        for s in _slabs(e, slice(top + R, Hkv))]
+            if n_dn > 0:
+                ops += [dist.P2POp(dist.irecv, s, _peer(group, shard.rank + 1), group)
+                        for s in _slabs(recv_dn[i], slice(0, n_dn))]
+    finish_exchange(dist.batch_isend_irecv(ops) if ops else [])
+    outs = []
+    for i, e in enumerate((dk_ext, dv_ext)):
+        local = e[:, :, top:top + R]
+        if n_up > 0:
+            local[:, :, :n_up] += recv_up[i]
+        if n_dn > 0:
+            local[:, :, R - n_dn:] += recv_dn[i]
+        outs.append(local.to(out_dtype or e.dtype).contiguous())
+    return outs[0], outs[1]
+
+
+def forward_band_into(ws: RowShardWorkspace, q, o, lse, kernel_size: int, group=None, scale: float = 1.0,
+                      path: str = "auto") -> None:
+    """Forward of this rank's band into caller-owned ``o`` (B, N, R, W, C) and ``lse`` (B, N, R, W),
+    K / V already in ``ws.k_local`` / ``ws.v_local``: starts the halo exchange, runs the interior
+    query rows meanwhile and the two boundary strips once the halo is there.  No autograd."""
+    sh = ws.shard
+    reqs = start_kv_halo_exchange(ws.k_ext, ws.v_ext, sh, group)
+    a, b = sh.top, sh.R - sh.bot
+    spans = [(a, b)]
+
+    def run(lo, hi):
+        part = torch.empty(lse.shape[:2] + (hi - lo, lse.shape[3]), dtype=torch.float32, device=lse.device)
+        F.forward_into(q[:, :, lo:hi], ws.k_ext, ws.v_ext, o[:, :, lo:hi], part, kernel_size, rows=sh.rows(lo, hi),
+                       path=path, scale=scale)
+        return part
+
+    parts = [run(a, b)]
+    finish_exchange(reqs)
+    if a > 0:
+        spans.append((0, a))
+        parts.append(run(0, a))
+    if b < sh.R:
+        spans.append((b, sh.R))
+        parts.append(run(b, sh.R))
+    for (lo, hi), part in zip(spans, parts):
+        lse[:, :, lo:hi].copy_(part)
+
+
+def backward_band_into(ws: RowShardWorkspace, q, o, lse, d_o, d_q, delta, kernel_size: int, group=None,
+                       scale: float = 1.0, path: str = "auto"):
+    """Backward of this rank's band: dQ into ``d_q``, the partial dK / dV of all extended rows in
+    fp32 into the workspace, then the halo reduction.  Returns (dK, dV) of the own rows."""
+    sh = ws.shard
+    dk_ext, dv_ext, recv_up, recv_dn = ws.partial_buffers()
+    rows = sh.rows()
+    F.backward_dq_into(q, ws.k_ext, ws.v_ext, o, lse, d_o, d_q, delta, kernel_size, rows=rows, path=path, scale=scale)
+    F.backward_dkdv_into(q, ws.k_ext, ws.v_ext, lse, d_o, delta, dk_ext, dv_ext, kernel_size, rows=rows, path=path,
+                         scale=scale)
+    return reduce_dkdv_halo(dk_ext, dv_ext, sh, group, out_dtype=ws.k_ext.dtype, recv=(recv_up, recv_dn))
 
 
 def _default_forward(q, k_ext, v_ext, ks, rows):
@@ -156,35 +284,60 @@ def _default_forward(q, k_ext, v_ext, ks, rows):
 
 
 def _default_backward(q, k_ext, v_ext, o, lse, d_o, ks, rows):
-    return F.natten2d_backward(q, k_ext, v_ext, o, lse, d_o, ks, rows=rows)
+    return F.natten2d_backward(q, k_ext, v_ext, o, lse, d_o, ks, rows=rows, dkdv_dtype=_partial_dtype(q.dtype))
 
 
 class RowShardedNatten2d(torch.autograd.Function):
     """``natten2d`` on one row band of an image that is split over the ranks of ``group``."""
 
     @staticmethod
-    def forward(ctx, q, k, v, kernel_size, shard: RowShard, group, forward_fn, backward_fn):
-        k_ext, v_ext = exchange_kv_halo(k.contiguous(), v.contiguous(), shard, group)
-        o, lse = (forward_fn or _default_forward)(q.contiguous(), k_ext, v_ext, kernel_size, shard.rows())
-        ctx.save_for_backward(q, k_ext, v_ext, o, lse)
-        ctx.kernel_size, ctx.shard, ctx.group, ctx.backward_fn = kernel_size, shard, group, backward_fn
+    def forward(ctx, q, k, v, kernel_size, shard: RowShard, group, forward_fn, backward_fn, workspace):
+        fwd = forward_fn or _default_forward
+        B, N, R, W, C = q.shape
+        ws = workspace
+        if ws is None or not ws.matches(k):
+            ws = RowShardWorkspace(shard, B, N, W, C, k.dtype, k.device)
+        for ext_local, t in ((ws.k_local, k), (ws.v_local, v)):
+            if t.data_ptr() != ext_local.data_ptr() or t.stride() != ext_local.stride():
+                ext_local.copy_(t)                     # K / V built elsewhere: one copy into the middle rows
+        reqs = start_kv_halo_exchange(ws.k_ext, ws.v_ext, shard, group)
+        # interior query rows see no halo row: their forward runs while the halo is on its way
+        a, b = shard.top, R - shard.bot
+        parts = [None, fwd(q[:, :, a:b], ws.k_ext, ws.v_ext, kernel_size, shard.rows(a, b)), None]
+        finish_exchange(reqs)
+        if a > 0:
+            parts[0] = fwd(q[:, :, :a], ws.k_ext, ws.v_ext, kernel_size, shard.rows(0, a))
+        if b < R:
+            parts[2] = fwd(q[:, :, b:], ws.k_ext, ws.v_ext, kernel_size, shard.rows(b, R))
+        parts = [p for p in parts if p is not None]
+        o = torch.cat([p[0] for p in parts], dim=2) if len(parts) > 1 else parts[0][0]
+        lse = torch.cat([p[1] for p in parts], dim=2) if len(parts) > 1 else parts[0][1]
+        ctx.save_for_backward(q, ws.k_ext, ws.v_ext, o, lse)
+        ctx.kernel_size, ctx.shard, ctx.group, ctx.backward_fn, ctx.ws = kernel_size, shard, group, backward_fn, ws
+        ctx.kv_dtype = k.dtype
         return o
 
     @staticmethod
     def backward(ctx, grad_output):
         q, k_ext, v_ext, o, lse = ctx.saved_tensors
         d_q, dk_ext, dv_ext = (ctx.backward_fn or _default_backward)(
-            q.contiguous(), k_ext, v_ext, o, lse, grad_output.contiguous(), ctx.kernel_size, ctx.shard.rows())
-        d_k, d_v = reduce_dkdv_halo(dk_ext, dv_ext, ctx.shard, ctx.group)
-        return d_q, d_k, d_v, None, None, None, None, None
+            q, k_ext, v_ext, o, lse, grad_output, ctx.kernel_size, ctx.shard.rows())
+        pd = _partial_dtype(ctx.kv_dtype)
+        if dk_ext.dtype != pd:                       # an injected backward that returns the tensors' dtype
+            dk_ext, dv_ext = dk_ext.to(pd), dv_ext.to(pd)
+        d_k, d_v = reduce_dkdv_halo(dk_ext, dv_ext, ctx.shard, ctx.group, out_dtype=ctx.kv_dtype)
+        return d_q, d_k, d_v, None, None, None, None, None, None
 
 
 def natten2d_row_sharded(q, k, v, kernel_size: int, H_global: int, group=None,
-                         forward_fn: Optional[Callable] = None, backward_fn: Optional[Callable] = None):
+                         forward_fn: Optional[Callable] = None, backward_fn: Optional[Callable] = None,
+                         workspace: Optional[RowShardWorkspace] = None):
     """Differentiable neighborhood attention over this rank's row band ``(B, N, R, W, C)`` of an
-    image of ``H_global`` rows split evenly (``plan_row_shard``) over the ranks of ``group``."""
+    image of ``H_global`` rows split evenly (``plan_row_shard``) over the ranks of ``group``.
+    ``workspace`` (optional) keeps the extended K / V buffers across steps; K / V that are its
+    ``k_local`` / ``v_local`` views are used in place."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     shard = plan_row_shard(H_global, world, rank, kernel_size)
     if q.shape[2] != shard.R:
         raise ValueError(f"rank {rank} must hold {shard.R} rows, got {q.shape[2]}")
-    return RowShardedNatten2d.apply(q, k, v, kernel_size, shard, group, forward_fn, backward_fn)
+    return RowShardedNatten2d.apply(q, k, v, kernel_size, shard, group, forward_fn, backward_fn, workspace)

@@ -152,6 +152,10 @@ int na2d_backward(const void* q, const void* k, const void* v, const void* o, co
  *             W = T, the row stride is ignored, the window is 1 x kernel_size, rows must be NULL.
  *   scale     logits are scale * (q . k); must be > 0; 1.0f reproduces the reference.
  *   o         output of the forward; optional input of the backward (see na2d_backward_dq).
+ *   flags     NA2D_FLAG_DKDV_F32: the key half writes dK and dV in fp32.  Meant for row views: the
+ *             dK / dV of a band are partial sums that their owner adds to its own, and partial
+ *             sums can be far larger than the total, so rounding each of them to 16 bits first
+ *             costs accuracy.
  *   lse       fp32 (B, N, Hq, W), dense: written by the forward, read by the backward.
  *   delta     fp32 (B, N, Hq, W), dense scratch of the backward.
  */
@@ -165,10 +169,14 @@ typedef enum na2d_op {
     NA2D_OP_1D = 1
 } na2d_op;
 
+/* na2d_args.flags */
+#define NA2D_FLAG_DKDV_F32 1   /* d_k, d_v are fp32 tensors (strides in fp32 elements) whatever `dtype` is */
+
 typedef struct na2d_args {
     size_t struct_size;
     int op;
     int B, N, H, W, C, kernel_size, dtype, path, device;
+    int flags;
     float scale;
     void* stream;
     const na2d_rows* rows;

@@ -13,14 +13,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def run_gpu(q, k, v, d_o, ks, path="auto", rows=None, with_o=True, scale=1.0):
+def run_gpu(q, k, v, d_o, ks, path="auto", rows=None, with_o=True, scale=1.0, dkdv_dtype=None):
     """(o, lse, dq, dk, dv) from the library's raw entry points.  `with_o`: hand the forward's
     output to the backward (what the autograd entry point does; the dQ kernel of the larger
     windows then takes its one-walk form); False runs the backward without it (two walks)."""
     qd, kd, vd, gd = (t.to(DEV) for t in (q, k, v, d_o))
     o, lse = na.natten2d_forward(qd, kd, vd, ks, rows=rows, path=path, scale=scale)
     dq, dk, dv = na.natten2d_backward(qd, kd, vd, o if with_o else None, lse, gd, ks, rows=rows, path=path,
-                                      scale=scale)
+                                      scale=scale, dkdv_dtype=dkdv_dtype)
     na.check_kernels(DEV)
     return o, lse, dq, dk, dv
 
@@ -253,7 +253,9 @@ def test_config5_huge_image_bands():
                                            (torch.float16, "auto", 5), (torch.bfloat16, "auto", 13)])
 def test_row_bands_reassemble_whole_image(dtype, path, ks):
     """Every kernel family under a row view with non-zero first rows: the strip kernels of kernel
-    sizes 3 and 5, the chunked kernels of the larger windows, and the SIMT kernels."""
+    sizes 3 and 5, the chunked kernels of the larger windows, and the SIMT kernels.  The bands'
+    dK / dV are partial sums, kept in fp32 as a row-sharded run keeps them: a partial sum can be
+    far larger than the total, and rounding each to 16 bits first would be the test's own error."""
     H, W = 45, 24
     q, k, v, d_o = make_inputs((2, 2, H, W, 64), dtype, 9)
     o, lse, dq, dk, dv = run_gpu(q, k, v, d_o, ks, path)
@@ -264,7 +266,8 @@ def test_row_bands_reassemble_whole_image(dtype, path, ks):
         kv1 = orc.window_start(e - 1, H, ks) + ks
         rows = na.make_rows(a, e - a, kv0, kv1 - kv0, H)
         ob, lb, dqb, dkb, dvb = run_gpu(q[:, :, a:e], k[:, :, kv0:kv1], v[:, :, kv0:kv1], d_o[:, :, a:e],
-                                        ks, path, rows=rows)
+                                        ks, path, rows=rows, dkdv_dtype=torch.float32)
+        assert dkb.dtype == torch.float32 and dvb.dtype == torch.float32
         if path == "simt":      # same arithmetic in the same order: bitwise equal
             assert torch.equal(ob, o[:, :, a:e]) and torch.equal(lb, lse[:, :, a:e])
             assert torch.equal(dqb, dq[:, :, a:e])

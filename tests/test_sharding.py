@@ -126,3 +126,52 @@ def test_missing_neighbour_is_an_error_not_a_hang():
         p.join(timeout=200)
     assert all(not p.is_alive() for p in procs)
     assert result.get(timeout=5).startswith("error")
+
+
+def _subgroup_worker(rank, world, port, result):
+    """The shard ranks live in a sub-group whose members are global ranks 1 and 2 (not 0 and 1):
+    the point-to-point peers must be translated from group ranks to global ranks.  Rank 0 of the
+    job does not take part.  A workspace keeps the extended K / V across two steps."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        group = dist.new_group(ranks=[1, 2])
+        err = 0.0
+        if rank >= 1:
+            H, W, ks = 22, 9, 7
+            q, k, v, d_o = orc.round_inputs((2, 1, H, W, 3), torch.float64, 29)
+            sh = sharding.plan_row_shard(H, 2, dist.get_rank(group), ks)
+            band = slice(sh.row0, sh.row0 + sh.R)
+            ws = sharding.RowShardWorkspace(sh, 2, 1, W, 3, torch.float64, "cpu")
+            ro, _, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks)
+            for step in range(2):
+                ws.k_local.copy_(k[:, :, band])                 # K / V built in place: no copy inside the call
+                ws.v_local.copy_(v[:, :, band])
+                ql = q[:, :, band].clone().requires_grad_()
+                kl, vl = ws.k_local.detach().requires_grad_(), ws.v_local.detach().requires_grad_()
+                o = sharding.natten2d_row_sharded(ql, kl, vl, ks, H, group=group, forward_fn=_oracle_forward,
+                                                  backward_fn=_oracle_backward, workspace=ws)
+                o.backward(d_o[:, :, band])
+                err = max(err, (o.detach() - ro[:, :, band]).abs().max().item(),
+                          (ql.grad - rdq[:, :, band]).abs().max().item(),
+                          (kl.grad - rdk[:, :, band]).abs().max().item(),
+                          (vl.grad - rdv[:, :, band]).abs().max().item())
+        errs = [None] * world
+        dist.all_gather_object(errs, err)
+        if rank == 0:
+            result.put(max(errs))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_sharding_inside_a_subgroup_that_does_not_start_at_rank_0():
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_subgroup_worker, args=(r, 3, port, result)) for r in range(3)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert result.get(timeout=5) < 1e-12
