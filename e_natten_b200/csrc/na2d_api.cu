@@ -100,12 +100,12 @@ int error_word_address(int device, unsigned int** out) {
 // The kernel of na2d_selftest_wait_timeout: one thread waits on a barrier nothing completes.
 __global__ void wait_timeout_kernel(unsigned int* err_word, unsigned long long limit_ns) {
     __shared__ uint64_t bar;
-    __shared__ uint32_t abort_flag;
+    __shared__ na2d_ptx::WaitState state;
     if (threadIdx.x == 0) {
-        abort_flag = 0;
+        na2d_ptx::wait_state_init(&state, err_word, limit_ns);
         na2d_ptx::mbar_init(&bar, 1);
         na2d_ptx::mbar_fence_init();
-        const na2d_ptx::WaitCtx wctx{&abort_flag, err_word, limit_ns};
+        const na2d_ptx::WaitCtx wctx{&state};
         na2d_ptx::mbar_wait(&bar, 0, wctx, na2d_ptx::kErrOther);
     }
 }
@@ -167,6 +167,7 @@ int make_problem(const na2d_args* a, Problem* out) {
     const bool one_d = a->op == NA2D_OP_1D;
     Na2dGeom g;
     g.BN = B * N; g.N = N; g.W = W; g.C = C; g.ks = ks; g.kh = one_d ? 1 : ks;
+    g.n_magic = na2d_heads_magic(g.BN, N);
     g.scale = a->scale;
     g.sl2 = a->scale * 1.4426950408889634f;
     if (one_d) {
@@ -439,7 +440,7 @@ int make_pair_problem(int B, int N, int H, int W, int C, int ks, int dtype, void
     if (H < ks || W < ks) return NA2D_ERR_WINDOW;
     if (C > na2d_simt::kMaxC || ks > na2d_simt::kMaxKs) return NA2D_ERR_UNSUPPORTED;
     Na2dGeom g;
-    g.BN = B * N; g.N = N; g.Hq = H; g.Hkv = H; g.W = W; g.C = C; g.ks = ks; g.kh = ks;
+    g.BN = B * N; g.N = N; g.n_magic = na2d_heads_magic(g.BN, N); g.Hq = H; g.Hkv = H; g.W = W; g.C = C; g.ks = ks; g.kh = ks;
     g.q_row0 = 0; g.kv_row0 = 0; g.Hg = H; g.scale = 1.f; g.sl2 = 1.4426950408889634f;
     out->g = g;
     out->dtype = dtype;

@@ -36,6 +36,7 @@ NA2D_HD int na2d_bwe(int j, int seq_len, int kernel_size) {
 struct Na2dGeom {
     int BN;        // batch * heads
     int N;         // heads (a unit index bn is batch bn / N, head bn % N)
+    unsigned n_magic;   // floor(2^32 / N) + 1 where bn / N == umulhi(bn, n_magic) for every unit, else 0
     int Hq;        // query-side rows held
     int Hkv;       // key-side rows held
     int W;         // grid columns
@@ -48,6 +49,13 @@ struct Na2dGeom {
     float scale;   // softmax scale: the logits are scale * (q . k)
     float sl2;     // scale * log2(e)
 };
+
+// Magic multiplier for unit_index / heads: with m = floor(2^32 / N) + 1, umulhi(x, m) == x / N for
+// every x with x * N < 2^32.  0 where that does not cover the units (or N == 1): divide then.
+NA2D_HD unsigned na2d_heads_magic(long long BN, int N) {
+    if (N <= 1 || BN * (long long)N >= (1ll << 32)) return 0u;
+    return (unsigned)((1ull << 32) / (unsigned long long)N) + 1u;
+}
 
 // Element strides of one (batch, heads, rows, columns, channels) tensor; the channel stride is 1.
 struct Na2dStride {

@@ -21,33 +21,42 @@ enum : unsigned int {
 // (a hint; the hardware may return earlier), so that waiting warps leave the issue slots of their
 // SM sub-partition to the warps that work (the MMA-issue warp shares its scheduler with softmax
 // warps).
-// A wait is bounded twice: by the time on the GPU's nanosecond timer (kWaitLimitNs, what ends a
-// wait in practice) and by a count of try_wait rounds (kSpinLimit, a backstop should the timer
-// not advance).  The time bound is what matters under a profiler: a replay pass that instruments
-// the kernel runs the working warps orders of magnitude slower, and a bound counted in rounds
-// alone (as it once was) ran out there although nothing was stuck.
+// A wait is bounded by real time (kWaitLimitNs), not by a number of polls alone: under a profiler
+// a replay pass that instruments the kernel runs the working warps orders of magnitude slower,
+// and a bound counted in plain polling rounds (as it once was) ran out there although nothing
+// was stuck.  Once the CTA has aborted, later waits end after their polling stage.
 constexpr uint32_t kWaitHintNs = 1000;
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s
-constexpr uint32_t kSpinLimit = 1u << 30;        // try_wait rounds, backstop only
-constexpr uint32_t kSpinLimitAborted = 1u << 8;  // once the CTA has aborted, later waits are short
-
-// What a bounded wait needs to report that it gave up: the CTA-shared abort flag (set by the
-// first waiter that gives up, it shortens every later wait of the CTA), the device error word
-// the host reads with na2d_check / na2d_poll, and the time limit of one wait.
-struct WaitCtx {
-    volatile uint32_t* abort_flag;
-    unsigned int* err_word;
-    unsigned long long limit_ns;
-};
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// What a bounded wait needs to report that it gave up, kept in shared memory (one per CTA, set up
+// by one thread before the first wait) so that a waiting thread carries a single pointer: the abort
+// flag (set by the first waiter that gives up, it shortens every later wait of the CTA), the device
+// error word the host reads with na2d_check / na2d_poll, and the time limit of one wait.
+struct WaitState {
+    uint32_t abort;
+    uint32_t limit_us;       // microseconds a wait may last
+    unsigned int* err_word;
+};
+struct WaitCtx {
+    WaitState* st;
+};
+// (accessors in the shared state space: a 32-bit address, no generic pointer kept in registers)
+__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void wait_state_init(WaitState* st, unsigned int* err_word, unsigned long long limit_ns) {
+    st->abort = 0;
+    st->limit_us = static_cast<uint32_t>(limit_ns / 1000ull);
+    st->err_word = err_word;
 }
 
 // ------------------------------------------------------------------------------------ mbarrier
@@ -91,57 +100,60 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Bounded wait.  Returns false if the wait gave up (after recording `err_code`).  The timer is
-// not touched during the first kTimerAfter rounds: nearly every wait ends within a few rounds,
-// and reading the global timer costs more than the rounds it would guard.
-constexpr uint32_t kTimerAfter = 1024;
-__device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const WaitCtx wc, unsigned int err_code) {
-    const bool aborted = *wc.abort_flag != 0;
-    const uint32_t limit = aborted ? kSpinLimitAborted : kSpinLimit;
-    unsigned long long t0 = 0;
-    for (uint32_t i = 0; i < limit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i >= kTimerAfter) {
-            if (i == kTimerAfter) t0 = global_timer_ns();
-            else if ((i & 127u) == 0 && global_timer_ns() - t0 > wc.limit_ns) break;
-            if (i > 4096) __nanosleep(32);
-        }
-    }
-    *wc.abort_flag = 1;
-    atomicOr(wc.err_word, err_code);
-    return false;
-}
+// Bounded wait.  Returns false if the wait gave up (after recording `err_code`).
+//
+// Three stages.  (1) One try_wait, which the hardware may hold for up to kWaitHintNs: most waits
+// end here.  (2) A plain polling loop of kPollRounds rounds.  (3) A wait that is still open after
+// that (about a millisecond) sleeps a microsecond between its polls and counts them: k rounds
+// mean that at least k microseconds of real time have passed, whatever slows the warps down, so
+// the count is the clock, and the wait gives up when it reaches the limit (or when the CTA has
+// aborted meanwhile).  None of the stages keeps anything alive but a counter: a waiting warp
+// usually sits among code with every register in use, and whatever a wait needed beyond that
+// (a 64-bit start time, say) would be spilled and reloaded around every wait that lasts - which
+// was measured as several per cent of the kernels' time.
+constexpr uint32_t kPollRounds = 1024;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& wc, unsigned int err_code) {
     if (mbar_try_wait(bar, parity)) return true;              // common case: already complete
-    return mbar_wait_slow(bar, parity, wc, err_code);
+#pragma unroll 1
+    for (uint32_t i = 0; i < kPollRounds; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint32_t st = smem_u32(wc.st);                      // {abort, limit_us, err_word}
+#pragma unroll 1
+    for (uint32_t i = 0; i < ld_shared_u32(st + 4) && ld_shared_u32(st) == 0; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(1000);
+    }
+    st_shared_u32(st, 1u);
+    atomicOr(wc.st->err_word, err_code);
+    return false;
 }
 
 // Book-keeping of a TMA producer: which load barriers it has armed last, so that a producer that
 // stops early (a wait for a free buffer gave up) can wait for the loads it has in flight before
 // the CTA exits - a bulk copy must not land in shared memory that no longer belongs to the CTA.
-template <int N>
+// All of a kernel's barriers sit in one array; a barrier is known here by its index in it, and the
+// state is two bit masks (armed, parity of the armed phase), so nothing leaves the registers.
 struct LoadTracker {
-    uint64_t* bar[N];
-    uint32_t par[N];
-    uint32_t armed = 0;
+    uint64_t* base;          // the kernel's barrier array (at most 32 entries)
+    uint32_t armed = 0, par = 0;
     bool ok = true;
+    __device__ __forceinline__ explicit LoadTracker(uint64_t* bars) : base(bars) {}
     // waits (bounded) until `empty` says the buffer is free; false once any wait has given up
     __device__ __forceinline__ bool acquire(uint64_t* empty, uint32_t parity, const WaitCtx& wc) {
         if (ok) ok = mbar_wait(empty, parity, wc, kErrLoadWait);
         return ok;
     }
-    __device__ __forceinline__ void arm(int slot, uint64_t* full, uint32_t parity, uint32_t bytes) {
-        bar[slot] = full;
-        par[slot] = parity;
-        armed |= 1u << slot;
+    __device__ __forceinline__ void arm(uint64_t* full, uint32_t parity, uint32_t bytes) {
+        const uint32_t bit = 1u << static_cast<uint32_t>(full - base);
+        armed |= bit;
+        par = parity ? (par | bit) : (par & ~bit);
         mbar_expect_tx(full, bytes);
     }
     // only after a give-up: every armed barrier completes when its bytes have landed
     __device__ __forceinline__ void drain(const WaitCtx& wc) {
         if (ok) return;
-#pragma unroll
-        for (int s = 0; s < N; ++s)
-            if ((armed >> s) & 1u) mbar_wait(bar[s], par[s], wc, kErrLoadWait);
+        for (uint32_t s = 0; s < 32; ++s)
+            if ((armed >> s) & 1u) mbar_wait(base + s, (par >> s) & 1u, wc, kErrLoadWait);
     }
 };
 

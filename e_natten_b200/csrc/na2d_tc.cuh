@@ -40,6 +40,12 @@ constexpr int TM = 128;    // queries (or keys) per tile = MMA M
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
+// Unit index bn -> head hn of batch hb.
+__device__ __forceinline__ void split_unit(int bn, const Na2dGeom& g, int& hn, int& hb) {
+    hb = g.n_magic ? (int)__umulhi((unsigned)bn, g.n_magic) : (g.N == 1 ? bn : bn / g.N);
+    hn = bn - hb * g.N;
+}
+
 // Compile-time geometry of one (head dim, kernel size) instantiation.
 // NMAX caps the keys (forward, dQ) or queries (dK/dV) of one chunk; it is set by how many
 // tensor-memory columns the kernel can spare for the S-shaped accumulators.
@@ -202,7 +208,7 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint8_t*
 // is 16 channels wide.
 template <int NCOL>
 __device__ __forceinline__ void stage_and_store_f32(const CUtensorMap* map, uint8_t* stage, const uint32_t (&v)[NCOL],
-                                                    int ch0, int w0, int h0, int n, int b, int lane) {
+                                                    float scale, int ch0, int w0, int h0, int n, int b, int lane) {
     static_assert(NCOL % 16 == 0, "rounds of 16 channels");
     const uint32_t row = smem_u32(stage) + lane * 64;
     const int sw = (lane >> 1) & 3;
@@ -212,8 +218,10 @@ __device__ __forceinline__ void stage_and_store_f32(const CUtensorMap* map, uint
         __syncwarp();
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-            st_shared_v4(row + ((c ^ sw) << 4), v[16 * r + 4 * c], v[16 * r + 4 * c + 1], v[16 * r + 4 * c + 2],
-                         v[16 * r + 4 * c + 3]);
+            st_shared_v4(row + ((c ^ sw) << 4), __float_as_uint(__uint_as_float(v[16 * r + 4 * c]) * scale),
+                         __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 1]) * scale),
+                         __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 2]) * scale),
+                         __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 3]) * scale));
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
@@ -364,7 +372,7 @@ struct LaunchCtx {
 // four warps of the data-movement group shrink to kRegsDonor, the eight softmax warps grow to
 // kRegsSoftmax.  setmaxnreg.inc blocks until the registers it asks for have been given up, so
 // what the eight warps take must not exceed what the four release.
-constexpr int kRegsLaunch = 168, kRegsDonor = 64, kRegsSoftmax = 216;
+constexpr int kRegsLaunch = 168, kRegsDonor = 72, kRegsSoftmax = 216;
 static_assert((kRegsSoftmax - kRegsLaunch) * 8 <= (kRegsLaunch - kRegsDonor) * 4, "setmaxnreg.inc would wait for ever");
 
 // The same for the kernels of sixteen warps (512 threads, launched with 128 registers each): softmax

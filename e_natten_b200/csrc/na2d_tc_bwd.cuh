@@ -5,17 +5,18 @@
 // tensor-memory lane r).  The tile's halo box of keys is taken in chunks of whole box rows.
 //     S = Q K_c^T,  dP = dO V_c^T                          (tensor memory, fp32)
 //     p = exp(S - lse),  delta = sum_j p dP                (softmax warps, registers)
-//     dS = scale p (dP - delta)  -> tensor memory, 16 bit  (head + residual on the bf16 path)
-//     dQ += dS K_c                                         (dS read from tensor memory)
+//     dS = p (dP - delta)  -> tensor memory, 16 bit        (head + residual on the bf16 path)
+//     dQ += dS K_c                                         (dS read from tensor memory; the softmax
+//                                                           scale is applied to the finished dQ)
 // delta needs every chunk of the tile before any dS can be formed exactly.  With one chunk (kernel
 // sizes up to 5: at most 256 keys) a tile is a single unit and dQ reuses the S columns.  With
 // several chunks there are two ways:
 //   * one walk with a correction.  The caller hands in an estimate d~ of delta (dO . o from the
 //     stored output, see na2d_delta.cuh; off by the rounding of o, a few 1e-2 at most).  Every
-//     unit forms dS~ = scale p (dP - d~), adds dS~ K_c to dQ and, with one more MMA, p K_c to a
+//     unit forms dS~ = p (dP - d~), adds dS~ K_c to dQ and, with one more MMA, p K_c to a
 //     second accumulator B, while the exact delta = sum_j p dP builds up in registers.  Since
 //     sum_j p (dP - delta) k = sum_j p (dP - d~) k - (delta - d~) sum_j p k, the epilogue stores
-//     dQ - scale (delta - d~) B.  B only meets the small factor (delta - d~), so a single 16-bit
+//     scale (dQ - (delta - d~) B).  B only meets the small factor (delta - d~), so a single 16-bit
 //     p is enough for it.  The exact delta is what the kernel writes out for the dK/dV kernel.
 //   * two walks (no estimate given): units 0..NCH-1 only add up delta, units NCH..2NCH-1 repeat
 //     the two score MMAs and accumulate dQ.
@@ -45,7 +46,10 @@ struct DqCfg : Cfg<D, KS, dq_nmax(D, KS)> {
     static constexpr int TMEM_PH = B::NKP / 2;                         // p (head): upper half of S (several chunks only)
     static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;       // output staging of the 8 softmax warps
     static constexpr int FIXED = 2 * B::Q_BYTES + OUT_BYTES + 2 * 2 * 128 * 4 /*delta exchange*/ + 256 + 1024;
-    static constexpr int SMEM = FIXED + 2 * B::KV_BYTES;               // one K chunk, one V chunk
+    // K and V chunk rings: two stages each where they fit, so that a chunk's loads run under the
+    // previous chunk's MMAs (a K chunk is only free again after the dQ MMAs that read it)
+    static constexpr int NST = (FIXED + 4 * B::KV_BYTES <= kSmemLimit) ? 2 : 1;
+    static constexpr int SMEM = FIXED + 2 * NST * B::KV_BYTES;
     static constexpr int NB16 = (B::NKP + 15) / 16;
     static_assert(SMEM <= kSmemLimit, "dQ kernel shared memory");
     static_assert(B::NKP <= NMAX, "tensor memory layout");
@@ -68,38 +72,40 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sDO = sQ + C::Q_BYTES;
-    uint8_t* sK = sDO + C::Q_BYTES;                   // key chunk   [NKP x D]
-    uint8_t* sV = sK + C::KV_BYTES;                   // value chunk [NKP x D]
-    uint8_t* sOut = sV + C::KV_BYTES;                 // 8 x output staging (1024-byte aligned)
+    constexpr int NST = C::NST;
+    uint8_t* sK = sDO + C::Q_BYTES;                   // NST x key chunk   [NKP x D]
+    uint8_t* sV = sK + NST * C::KV_BYTES;             // NST x value chunk [NKP x D]
+    uint8_t* sOut = sV + NST * C::KV_BYTES;           // 8 x output staging (1024-byte aligned)
     float* x_sum = reinterpret_cast<float*>(sOut + C::OUT_BYTES);     // [tile parity][half][row]
     uint64_t* bars = reinterpret_cast<uint64_t*>(x_sum + 2 * 2 * 128);
     uint64_t* q_full = bars + 0;             // TMA -> MMA (Q and dO tile)
     uint64_t* q_empty = bars + 1;            // MMA (commit) -> TMA
-    uint64_t* k_full = bars + 2;
-    uint64_t* k_empty = bars + 3;
-    uint64_t* v_full = bars + 4;
-    uint64_t* v_empty = bars + 5;
-    uint64_t* s_full = bars + 6;             // MMA (commit) -> softmax: S and dP are complete
-    uint64_t* s_free = bars + 7;             // softmax -> MMA: S and dP have been read (delta-only units)
-    uint64_t* p_full = bars + 8;             // softmax -> MMA: dS is in tensor memory
-    uint64_t* dq_full = bars + 9;            // MMA (commit) -> softmax (epilogue)
-    uint64_t* dq_free = bars + 10;           // softmax -> MMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
+    uint64_t* k_full = bars + 2;             // [2]
+    uint64_t* k_empty = bars + 4;            // [2]
+    uint64_t* v_full = bars + 6;             // [2]
+    uint64_t* v_empty = bars + 8;            // [2]
+    uint64_t* s_full = bars + 10;            // MMA (commit) -> softmax: S and dP are complete
+    uint64_t* s_free = bars + 11;            // softmax -> MMA: S and dP have been read (delta-only units)
+    uint64_t* p_full = bars + 12;            // softmax -> MMA: dS is in tensor memory
+    uint64_t* dq_full = bars + 13;           // MMA (commit) -> softmax (epilogue)
+    uint64_t* dq_free = bars + 14;           // softmax -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    const WaitCtx wctx{reinterpret_cast<WaitState*>(bars + 16)};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const bool want_dq = want_dq_arg != 0;
 
     if (tid == 0) {
-        *abort_flag = 0;
+        wait_state_init(wctx.st, err_word, kWaitLimitNs);
         mbar_init(q_full, 1);
         mbar_init(q_empty, 1);
-        mbar_init(k_full, 1);
-        mbar_init(k_empty, 1);
-        mbar_init(v_full, 1);
-        mbar_init(v_empty, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + i, 1);
+            mbar_init(k_empty + i, 1);
+            mbar_init(v_full + i, 1);
+            mbar_init(v_empty + i, 1);
+        }
         mbar_init(s_full, 1);
         mbar_init(s_free, 8);
         mbar_init(p_full, 8);
@@ -117,12 +123,13 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
-    // K rows [NK, NKP) are contraction rows of dQ = dS K that TMA never writes: zero them once.
+    // K rows [NK, NKP) of every stage are contraction rows of dQ = dS K that TMA never writes: zero them once.
     if constexpr (C::NKP > C::NK) {
         constexpr int pad16 = (C::NKP - C::NK) * C::ROWB / 16;
-        for (int i = tid; i < C::NS * pad16; i += 384) {
-            const int slab = i / pad16, off = i - slab * pad16;
-            st_shared_v4(smem_u32(sK + slab * C::KV_SLAB + C::NK * C::ROWB + off * 16), 0u, 0u, 0u, 0u);
+        for (int i = tid; i < NST * C::NS * pad16; i += 384) {
+            const int which = i / pad16, off = i - which * pad16;             // which = stage * NS + slab
+            st_shared_v4(smem_u32(sK + (which / C::NS) * C::KV_BYTES + (which % C::NS) * C::KV_SLAB + C::NK * C::ROWB +
+                                  off * 16), 0u, 0u, 0u, 0u);
         }
         fence_proxy_async();
     }
@@ -131,16 +138,15 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // my i-th tile: unit bn = head hn of batch hb, first row r0, first column c0
-    auto decode = [&](int i, int& bn, int& hn, int& hb, int& r0, int& c0) {
+    // my i-th tile: unit bn (head bn % N of batch bn / N, split where a TMA coordinate needs it),
+    // first row r0, first column c0
+    auto decode = [&](int i, int& bn, int& r0, int& c0) {
         int t = (int)blockIdx.x + i * (int)gridDim.x;
         const int tc = t % tiles_c;
         t /= tiles_c;
         r0 = (t % tiles_r) * TH;
         c0 = tc * TW;
         bn = t / tiles_r;
-        hb = bn / g.N;
-        hn = bn - hb * g.N;
     };
     // A unit u of a tile works on chunk u % NCH.  Units from first_ds on form dS and add to dQ; the
     // units before it (a first walk, only when no estimate of delta is given) add up delta.
@@ -154,14 +160,15 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
         reg_dec<kRegsDonor>();
         if (lane == 0) {
             uint32_t n = 0;
-            LoadTracker<3> lt;                                   // slots: Q / dO tile, V chunk, K chunk
+            LoadTracker lt(bars);
             for (int i = 0; i < n_my && lt.ok; ++i) {
-                int bn, hn, hb, r0, c0;
-                decode(i, bn, hn, hb, r0, c0);
+                int bn, r0, c0, hn, hb;
+                decode(i, bn, r0, c0);
+                split_unit(bn, g, hn, hb);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
                 if (!lt.acquire(q_empty, (i & 1) ^ 1, wctx)) break;
-                lt.arm(0, q_full, i & 1, 2u * C::Q_BYTES);
+                lt.arm(q_full, i & 1, 2u * C::Q_BYTES);
 #pragma unroll
                 for (int s = 0; s < C::NS; ++s) {
                     tma_load_5d(sQ + s * C::Q_SLAB, &tm_q, q_full, s * 64, c0, r0, hn, hb);
@@ -169,16 +176,19 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 }
                 for (int u = 0; u < units_run; ++u, ++n) {
                     const int c = u % NCH;
-                    if (!lt.acquire(v_empty, (n & 1) ^ 1, wctx)) break;
-                    lt.arm(1, v_full, n & 1, (uint32_t)C::NS * C::NK * C::ROWB);
+                    const uint32_t st = n % NST, par = (n / NST) & 1;
+                    if (!lt.acquire(v_empty + st, par ^ 1, wctx)) break;
+                    lt.arm(v_full + st, par, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
-                        tma_load_5d(sV + s * C::KV_SLAB, &tm_v, v_full, s * 64, box_c0, box_r0 + c * C::RC, hn, hb);
-                    if (!lt.acquire(k_empty, (n & 1) ^ 1, wctx)) break;
-                    lt.arm(2, k_full, n & 1, (uint32_t)C::NS * C::NK * C::ROWB);
+                        tma_load_5d(sV + st * C::KV_BYTES + s * C::KV_SLAB, &tm_v, v_full + st, s * 64, box_c0,
+                                    box_r0 + c * C::RC, hn, hb);
+                    if (!lt.acquire(k_empty + st, par ^ 1, wctx)) break;
+                    lt.arm(k_full + st, par, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
-                        tma_load_5d(sK + s * C::KV_SLAB, &tm_k, k_full, s * 64, box_c0, box_r0 + c * C::RC, hn, hb);
+                        tma_load_5d(sK + st * C::KV_BYTES + s * C::KV_SLAB, &tm_k, k_full + st, s * 64, box_c0,
+                                    box_r0 + c * C::RC, hn, hb);
                 }
             }
             lt.drain(wctx);
@@ -191,16 +201,18 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
         constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
         constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
         const uint32_t q_lo = smem_desc_lo(smem_u32(sQ), 16), g_lo = smem_desc_lo(smem_u32(sDO), 16);
-        const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16), v_lo = smem_desc_lo(smem_u32(sV), 16);
-        const uint32_t km_lo = smem_desc_lo(smem_u32(sK), C::KV_SLAB);
         uint32_t n = 0, n_free = 0, n_p = 0;          // units, delta-only units, dS units so far
         for (int i = 0; i < n_my; ++i) {
             mbar_wait(q_full, i & 1, wctx, kErrLoadWait);
             for (int u = 0; u < units_run; ++u, ++n) {
                 const bool forms_ds = want_dq && u >= first_ds;
+                const uint32_t st = n % NST, par = (n / NST) & 1;
+                const uint32_t k_lo = smem_desc_lo(smem_u32(sK + st * C::KV_BYTES), 16);
+                const uint32_t v_lo = smem_desc_lo(smem_u32(sV + st * C::KV_BYTES), 16);
+                const uint32_t km_lo = smem_desc_lo(smem_u32(sK + st * C::KV_BYTES), C::KV_SLAB);
                 if (leader) NA2D_TR(2, 0, n);
-                mbar_wait(k_full, n & 1, wctx, kErrLoadWait);
-                mbar_wait(v_full, n & 1, wctx, kErrLoadWait);
+                mbar_wait(k_full + st, par, wctx, kErrLoadWait);
+                mbar_wait(v_full + st, par, wctx, kErrLoadWait);
                 // the accumulators the score MMAs overwrite must have been read
                 if (u > 0 && !(want_dq && u - 1 >= first_ds)) {  // previous unit was delta-only
                     mbar_wait(s_free, (n_free & 1) ^ 1, wctx, kErrMmaWait);
@@ -231,8 +243,8 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                                 desc64(hi, v_lo + ((slab * C::KV_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
                     }
                     umma_commit(s_full);
-                    umma_commit(v_empty);
-                    if (!forms_ds) umma_commit(k_empty);
+                    umma_commit(v_empty + st);
+                    if (!forms_ds) umma_commit(k_empty + st);
                     if (u == units_run - 1) umma_commit(q_empty);     // last score MMAs of the tile
                     NA2D_TR(2, 2, n);
                 }
@@ -261,7 +273,7 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                             umma_ts(tmem_base + C::TMEM_BK, tmem_base + C::TMEM_PH + 8 * kk,
                                     desc64(hi, km_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
                     }
-                    umma_commit(k_empty);
+                    umma_commit(k_empty + st);
                     if (u == units_run - 1) umma_commit(dq_full);
                     NA2D_TR(2, 4, n);
                 }
@@ -284,8 +296,8 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 
         uint32_t n = 0, n_x = 0;                             // units, delta exchanges so far
         for (int i = 0; i < n_my; ++i) {
-            int bn, hn, hb, r0, c0;
-            decode(i, bn, hn, hb, r0, c0);
+            int bn, r0, c0;
+            decode(i, bn, r0, c0);
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
             const int qr_raw = r0 + (row / TW), qc_raw = c0 + (row % TW);
@@ -380,9 +392,9 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                     continue;
                 }
 
-                // dS = scale * p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path);
+                // dS = p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path);
                 // with the one-walk scheme delta is the estimate, and p goes along as a third operand
-                const float dls = (given ? d_est : dl) * g.scale;
+                const float dlu = given ? d_est : dl;
 #pragma unroll
                 for (int a = 0; a < NACT; ++a) {
                     const int blk = half + 2 * (bi_lo + a);
@@ -391,9 +403,9 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
 #pragma unroll
                         for (int e2 = 0; e2 < 8; ++e2) {
                             const float ds0 = ((vmask[a] >> (2 * e2)) & 1u)
-                                ? __uint_as_float(s[a][2 * e2]) * fmaf(__uint_as_float(dp[a][2 * e2]), g.scale, -dls) : 0.f;
+                                ? __uint_as_float(s[a][2 * e2]) * (__uint_as_float(dp[a][2 * e2]) - dlu) : 0.f;
                             const float ds1 = ((vmask[a] >> (2 * e2 + 1)) & 1u)
-                                ? __uint_as_float(s[a][2 * e2 + 1]) * fmaf(__uint_as_float(dp[a][2 * e2 + 1]), g.scale, -dls) : 0.f;
+                                ? __uint_as_float(s[a][2 * e2 + 1]) * (__uint_as_float(dp[a][2 * e2 + 1]) - dlu) : 0.f;
                             wd[e2] = pack2<DT>(ds0, ds1);
                             wr2[e2] = SPLIT ? pack2_residual_bf16(ds0, ds1, wd[e2]) : 0u;
                         }
@@ -437,8 +449,8 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                     tmem_ld_32x16(tmem_lane + C::TMEM_DQ + half * DH + 16 * piece,
                                   *reinterpret_cast<uint32_t(*)[16]>(&acc[16 * piece]));
                 if (given) {
-                    // dQ - scale (delta - estimate) B, piece by piece
-                    const float corr = (dl - d_est) * g.scale;
+                    // dQ - (delta - estimate) B, piece by piece
+                    const float corr = dl - d_est;
 #pragma unroll
                     for (int piece = 0; piece < DH / 16; ++piece) {
                         uint32_t bk[16];
@@ -454,7 +466,9 @@ dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUte
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dq_free);
                 if (tid == 0) NA2D_TR(3, 6, n - 1);
-                stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0,
+                int hn, hb;
+                split_unit(bn, g, hn, hb);
+                stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, g.scale, half * DH, c0,
                                         r0 + quarter * (32 / TW), hn, hb, lane);
                 if (tid == 0) NA2D_TR(3, 7, n - 1);
             }

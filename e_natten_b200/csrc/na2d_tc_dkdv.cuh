@@ -89,14 +89,13 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     uint64_t* qd_empty = bars + 12;          // [4]   MMA (commit) -> TMA
     uint64_t* st_free = bars + 16;           // [2]   output MMAs (commit) -> score MMAs: the stage is free
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
+    const WaitCtx wctx{reinterpret_cast<WaitState*>(bars + 19)};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
     if (tid == 0) {
-        *abort_flag = 0;
+        wait_state_init(wctx.st, err_word, kWaitLimitNs);
         mbar_init(kv_full, 1);
         mbar_init(kv_empty, 1);
         mbar_init(acc_full, 1);
@@ -150,8 +149,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         t.kr0 = (x % tiles_r) * TH;
         t.kc0 = tc * TW;
         t.bn = x / tiles_r;
-        t.hb = t.bn / g.N;
-        t.hn = t.bn - t.hb * g.N;
+        split_unit(t.bn, g, t.hn, t.hb);
         const int kg_first = g.kv_row0 + t.kr0;
         const int kg_last = g.kv_row0 + min(t.kr0 + TH, g.Hkv) - 1;
         t.qb_r0 = max(na2d_bws(kg_first, KS), g.q_row0);                           // global row
@@ -172,7 +170,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
             uint32_t n = 0;
-            LoadTracker<4> lt;                                   // slots: the ring's stages
+            LoadTracker lt(bars);
             for (int i = 0; i < n_my && lt.ok; ++i) {
                 const TileGeo t = tile_geo(i);
                 for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
@@ -180,7 +178,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     const uint32_t st = n % NSTQ;
                     if (!lt.acquire(qd_empty + st, ((n / NSTQ) & 1) ^ 1, wctx)) break;
                     NA2D_TR(2, 7, n);
-                    lt.arm(st, qd_full + st, (n / NSTQ) & 1, 2u * C::NS * C::NK * C::ROWB);
+                    lt.arm(qd_full + st, (n / NSTQ) & 1, 2u * C::NS * C::NK * C::ROWB);
                     uint8_t* dst = sQD + st * C::STAGE;
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s) {
@@ -288,12 +286,12 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
             uint32_t it = 0;                            // non-empty tile counter
-            LoadTracker<1> lt;
+            LoadTracker lt(bars);
             for (int i = 0; i < n_my; ++i) {
                 const TileGeo t = tile_geo(i);
                 if (t.n_ch == 0) continue;
                 if (!lt.acquire(kv_empty, (it & 1) ^ 1, wctx)) break;
-                lt.arm(0, kv_full, it & 1, 2u * C::Q_BYTES);
+                lt.arm(kv_full, it & 1, 2u * C::Q_BYTES);
 #pragma unroll
                 for (int s = 0; s < C::NS; ++s) {
                     tma_load_5d(sK + s * C::Q_SLAB, &tm_k, kv_full, s * 64, t.kc0, t.kr0, t.hn, t.hb);
@@ -320,7 +318,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
 #pragma unroll
                 for (int j = 0; j < 2 * RPO; ++j) {
                     if (f32_out)
-                        stage_and_store_f32<32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 32 * (j % RPO), t.kc0,
+                        stage_and_store_f32<32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
                                                 t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane);
                     else
                         stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
@@ -348,12 +346,14 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     if (lane == 0) mbar_arrive(acc_free);
                     if (warp == 12 && lane == 0) NA2D_TR(0, 2, it);
                 }
+                // dK = scale * sum_i p (dP - delta) q: the softmax scale goes in here, once per output
+                const float out_scale = j / RPO == 0 ? 1.f : g.scale;
                 if (f32_out)
-                    stage_and_store_f32<32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 32 * (j % RPO), t.kc0, h0,
-                                            t.hn, t.hb, lane);
+                    stage_and_store_f32<32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], out_scale, 32 * (j % RPO), t.kc0,
+                                            h0, t.hn, t.hb, lane);
                 else
-                    stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 1.f, 32 * (j % RPO), t.kc0, h0,
-                                            t.hn, t.hb, lane);
+                    stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], out_scale, 32 * (j % RPO), t.kc0,
+                                            h0, t.hn, t.hb, lane);
             }
             if (warp == 12 && lane == 0) NA2D_TR(0, 3, it);
             ++it;
@@ -401,7 +401,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     if (br < t.n_rows && qc < g.W) {
                         const size_t qi = (static_cast<size_t>(t.bn) * g.Hq + (t.q_local_r0 + br)) * g.W + qc;
                         l2 = lse[qi] * kLog2e;
-                        dl = delta[qi] * g.scale;      // dS carries the softmax scale: dK = scale * sum_i p (dP - delta) q
+                        dl = delta[qi];
                     }
                     x_lse[gtid] = l2;
                     x_delta[gtid] = dl;
@@ -471,7 +471,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                                 const float pe = fast_exp2(fmaf(__uint_as_float(s[a][e]), g.sl2, -l2[e]));
                                 const bool ok = (vmask[a] >> e) & 1u;      // select, never multiply by zero
                                 p[h] = ok ? pe : 0.f;
-                                ds[h] = ok ? pe * fmaf(__uint_as_float(dp[a][e]), g.scale, -dl[e]) : 0.f;
+                                ds[h] = ok ? pe * (__uint_as_float(dp[a][e]) - dl[e]) : 0.f;
                             }
                             wp[e2] = pack2<DT>(p[0], p[1]);
                             wd[e2] = pack2<DT>(ds[0], ds[1]);

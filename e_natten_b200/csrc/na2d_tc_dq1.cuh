@@ -58,14 +58,13 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     uint64_t* st_full = bars + 8;            // [4]  TMA -> MMA, per strip buffer
     uint64_t* st_empty = bars + 12;          // [4]  MMA (commit) -> TMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
+    const WaitCtx wctx{reinterpret_cast<WaitState*>(bars + 17)};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
     if (tid == 0) {
-        *abort_flag = 0;
+        wait_state_init(wctx.st, err_word, kWaitLimitNs);
         mbar_init(q_full, 1);
         mbar_init(q_empty, 1);
         mbar_init(dq_full, 1);
@@ -106,16 +105,15 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // my i-th tile: unit bn = head hn of batch hb, first row r0, first column c0
-    auto decode = [&](int i, int& bn, int& hn, int& hb, int& r0, int& c0) {
+    // my i-th tile: unit bn (head bn % N of batch bn / N, split where a TMA coordinate needs it),
+    // first row r0, first column c0
+    auto decode = [&](int i, int& bn, int& r0, int& c0) {
         int t = (int)blockIdx.x + i * (int)gridDim.x;
         const int tc = t % tiles_c;
         t /= tiles_c;
         r0 = (t % tiles_r) * TH;
         c0 = tc * TW;
         bn = t / tiles_r;
-        hb = bn / g.N;
-        hn = bn - hb * g.N;
     };
     // Strip buffers of tile i: every tile the roles rotate (K_A, V_A, K_B, V_B) <- (V_A, V_B, K_A, K_B),
     // a cycle of length four.  Each buffer is filled and released exactly once per tile, so the
@@ -132,16 +130,17 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         // ------------------------------------------------------------------ producer
         reg_dec<kRegsDonor>();
         if (lane == 0) {
-            LoadTracker<5> lt;                                   // slots: strip buffers 0-3, Q / dO tile 4
+            LoadTracker lt(bars);
             for (int i = 0; i < n_my && lt.ok; ++i) {
-                int bn, hn, hb, r0, c0;
-                decode(i, bn, hn, hb, r0, c0);
+                int bn, r0, c0, hn, hb;
+                decode(i, bn, r0, c0);
+                split_unit(bn, g, hn, hb);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
                 const Slots s = slots_of(i);
                 const uint32_t par_free = (i & 1) ^ 1;
                 if (!lt.acquire(q_empty, par_free, wctx)) break;
-                lt.arm(4, q_full, i & 1, 2u * C::Q_BYTES);
+                lt.arm(q_full, i & 1, 2u * C::Q_BYTES);
 #pragma unroll
                 for (int sl = 0; sl < C::NS; ++sl) {
                     tma_load_5d(sQ + sl * C::Q_SLAB, &tm_q, q_full, sl * 64, c0, r0, hn, hb);
@@ -152,7 +151,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     if (!lt.acquire(st_empty + slot[j], par_free, wctx)) break;
-                    lt.arm(slot[j], st_full + slot[j], i & 1, (uint32_t)C::NS * C::NK * C::ROWB);
+                    lt.arm(st_full + slot[j], i & 1, (uint32_t)C::NS * C::NK * C::ROWB);
                     uint8_t* dst = sStrip + slot[j] * C::KV_BYTES;
                     // (the tensor map is named in each call: a map chosen through a run-time pointer
                     // may be copied to local memory, where TMA cannot read it)
@@ -262,8 +261,8 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         constexpr unsigned long long kRepLo = C::REP_LO, kRepHi = C::REP_HI;   // bit r * HW for the ks window rows
 
         for (int i = 0; i < n_my; ++i) {
-            int bn, hn, hb, r0, c0;
-            decode(i, bn, hn, hb, r0, c0);
+            int bn, r0, c0;
+            decode(i, bn, r0, c0);
             const uint32_t par = i & 1;
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
@@ -355,7 +354,6 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             bar_sync(1 + quarter, 64);
             const float dl = (d0 + d1) + x_sum[(par * 2 + (half ^ 1)) * 128 + row];
             if (q_valid && half == 0) delta[qi] = dl;
-            const float dls = dl * g.scale;                  // dS carries the softmax scale: dQ = scale * sum_j p (dP - delta) k
 
             // dS = p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path)
 #pragma unroll
@@ -369,8 +367,8 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                         for (int e2 = 0; e2 < 8; ++e2) {
                             // p and dP of masked columns are exact zeros here
-                            const float ds0 = __uint_as_float(s[x][a][2 * e2]) * fmaf(__uint_as_float(dp[x][a][2 * e2]), g.scale, -dls);
-                            const float ds1 = __uint_as_float(s[x][a][2 * e2 + 1]) * fmaf(__uint_as_float(dp[x][a][2 * e2 + 1]), g.scale, -dls);
+                            const float ds0 = __uint_as_float(s[x][a][2 * e2]) * (__uint_as_float(dp[x][a][2 * e2]) - dl);
+                            const float ds1 = __uint_as_float(s[x][a][2 * e2 + 1]) * (__uint_as_float(dp[x][a][2 * e2 + 1]) - dl);
                             wd[e2] = pack2<DT>(ds0, ds1);
                             wr2[e2] = SPLIT ? pack2_residual_bf16(ds0, ds1, wd[e2]) : 0u;
                         }
@@ -408,7 +406,10 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) mbar_arrive(dq_free);
             if (tid == 0) NA2D_TR(3, 7, i);
-            stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0, r0 + quarter * (32 / TW), hn, hb,
+            // dQ = scale * sum_j p (dP - delta) k: the softmax scale goes in here, once per output
+            int hn, hb;
+            split_unit(bn, g, hn, hb);
+            stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, g.scale, half * DH, c0, r0 + quarter * (32 / TW), hn, hb,
                                     lane);
         }
         if (lane == 0) bulk_wait<0>();          // the staging buffer has been read, the rows written

@@ -1,8 +1,9 @@
-// Persistent, warp-specialised tcgen05 forward kernel.  Included by na2d_tc.cuh.
+// Persistent, warp-specialised tcgen05 forward kernel for the larger windows (kernel sizes >= 7).
+// Included by na2d_tc_fwd.cu.
 //
 // One CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  A tile is TH x TW queries;
-// its halo box of keys is taken in chunks of whole box rows with at most 256 keys (one chunk for
-// kernel sizes up to 5).  Twelve warps in three groups of four:
+// its halo box of keys is taken in chunks of whole box rows with at most 192 keys.  Twelve warps
+// in three groups of four:
 //   warps 0-7  softmax.  Warps w and w+4 own the same 32 queries (tensor-memory lanes
 //              32*(w%4)..) and split the 16-column blocks of S between them (even / odd); they
 //              read their blocks of S from tensor memory once, exchange the row maximum through
@@ -11,11 +12,16 @@
 //              tensor memory across the chunks of a tile and is rescaled there only when a row's
 //              maximum grows by more than 2^8 (until then the older maximum keeps being used,
 //              which leaves the result unchanged).  The tile's epilogue (normalise, store o and
-//              lse) is deferred into the next tile, whose S MMA and loads it overlaps.
+//              lse) is deferred into the next tile, whose MMAs and loads it overlaps.
 //   warp 8     producer: TMA loads of Q tiles (two buffers), K chunks and V chunks (separate
 //              rings: a K slot is free again as soon as S = Q K^T has been computed);
 //   warp 9     MMA issue: S = Q K^T, then O += P V with P read from tensor memory;
 //   warps 10-11 idle (they fill the third group, which hands its registers to warps 0-7).
+// Tensor memory holds two S / P buffers, so the tensor pipe computes the scores of chunk n+1 (and
+// n+2, once P V of chunk n has left its buffer) while the softmax warps work on chunk n: on the
+// pipe the order is S(0) S(1) | PV(0) S(2) | PV(1) S(3) | ...  The rest holds the output
+// accumulator, twice where the head dim leaves room (the epilogue of tile t then never holds up
+// the first P V of tile t+1).
 // Shared-memory traffic is what the design economises: every UMMA with both operands in shared
 // memory re-reads a 128-row A operand, so S is computed with the widest N that fits and P never
 // touches shared memory.  Every hand-over is an mbarrier with a bounded wait.
@@ -27,8 +33,8 @@ namespace na2d_tc {
 
 
 template <int D, int KS>
-struct FwdCfg : Cfg<D, KS, 256> {
-    using B = Cfg<D, KS, 256>;
+struct FwdCfg : Cfg<D, KS, 192> {
+    using B = Cfg<D, KS, 192>;
     // The K chunk keeps only the rows TMA writes (rounded to the swizzle period): the UMMA reads
     // NKP rows, and the few it reads past the end only feed S columns that are masked anyway.
     // The V chunk keeps all NKP rows, the padding ones zeroed, because they are contraction rows.
@@ -50,9 +56,11 @@ struct FwdCfg : Cfg<D, KS, 256> {
     static constexpr int NQ = fits(2, NSTK, NSTV) ? 2 : 1;
     static constexpr int SMEM = FIXED + NQ * B::Q_BYTES + NSTK * K_BYTES + NSTV * V_BYTES;
     static constexpr int NB16 = (B::NKP + 15) / 16;                     // 16-column blocks of S
-    static constexpr int TMEM_S = 0, TMEM_O0 = 256, TMEM_OSTRIDE = 128; // S / P at 0, O[2] at 256 / 384
+    static constexpr int TMEM_S = 0, TMEM_SSTRIDE = 192;                // two S / P buffers at 0 and 192
+    static constexpr int TMEM_O0 = 384, TMEM_OSTRIDE = D;               // O at 384 (and 384 + D where it fits)
+    static constexpr int NOB = (TMEM_O0 + 2 * D <= 512) ? 2 : 1;
     static_assert(SMEM <= kSmemLimit, "forward kernel shared memory");
-    static_assert(B::NKP <= 256 && D <= 128, "tensor memory layout");
+    static_assert(B::NKP <= 192 && TMEM_O0 + NOB * D <= 512, "tensor memory layout");
 };
 
 template <typename DT, int D, int KS>
@@ -80,19 +88,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     uint64_t* k_empty = bars + 10;           // [2]   MMA (commit) -> TMA
     uint64_t* v_full = bars + 12;            // [2]   TMA -> MMA
     uint64_t* v_empty = bars + 14;           // [2]   MMA (commit) -> TMA
-    uint64_t* s_full = bars + 16;            //       MMA (commit) -> softmax
-    uint64_t* p_full = bars + 17;            //       softmax -> MMA
-    uint64_t* pv_done = bars + 18;           //       MMA (commit) -> softmax: O holds this chunk
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
+    uint64_t* s_full = bars + 16;            // [2]   MMA (commit) -> softmax, per S buffer
+    uint64_t* p_full = bars + 18;            // [2]   softmax -> MMA, per S buffer
+    uint64_t* pv_done = bars + 20;           //       MMA (commit) -> softmax: O holds this chunk
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+    const WaitCtx wctx{reinterpret_cast<WaitState*>(bars + 22)};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const uint32_t total_units = (uint32_t)n_my * C::NCH;
 
     if (tid == 0) {
-        *abort_flag = 0;
+        wait_state_init(wctx.st, err_word, kWaitLimitNs);
         for (int i = 0; i < 2; ++i) {
             mbar_init(q_full + i, 1);
             mbar_init(q_empty + i, 1);
@@ -102,9 +109,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             mbar_init(k_empty + i, 1);
             mbar_init(v_full + i, 1);
             mbar_init(v_empty + i, 1);
+            mbar_init(s_full + i, 1);
+            mbar_init(p_full + i, 8);
         }
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 8);
         mbar_init(pv_done, 1);
         mbar_fence_init();
         tma_prefetch_desc(&tm_q);
@@ -133,16 +140,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // my i-th tile: unit bn = head hn of batch hb, first row r0, first column c0
-    auto decode = [&](int i, int& bn, int& hn, int& hb, int& r0, int& c0) {
+    // my i-th tile: unit bn (head bn % N of batch bn / N, split where a TMA coordinate needs it),
+    // first row r0, first column c0
+    auto decode = [&](int i, int& bn, int& r0, int& c0) {
         int t = (int)blockIdx.x + i * (int)gridDim.x;
         const int tc = t % tiles_c;
         t /= tiles_c;
         r0 = (t % tiles_r) * TH;
         c0 = tc * TW;
         bn = t / tiles_r;
-        hb = bn / g.N;
-        hn = bn - hb * g.N;
     };
 
     if (warp == 8) {
@@ -150,15 +156,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         reg_dec<kRegsDonor>();
         if (lane == 0) {
             uint32_t n = 0;
-            LoadTracker<6> lt;                                  // slots: Q 0-1, K 2-3, V 4-5
+            LoadTracker lt(bars);
             for (int i = 0; i < n_my && lt.ok; ++i) {
-                int bn, hn, hb, r0, c0;
-                decode(i, bn, hn, hb, r0, c0);
+                int bn, r0, c0, hn, hb;
+                decode(i, bn, r0, c0);
+                split_unit(bn, g, hn, hb);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
                 const int qb = i % NQ;
                 if (!lt.acquire(q_empty + qb, ((i / NQ) & 1) ^ 1, wctx)) break;
-                lt.arm(qb, q_full + qb, (i / NQ) & 1, C::Q_BYTES);
+                lt.arm(q_full + qb, (i / NQ) & 1, C::Q_BYTES);
 #pragma unroll
                 for (int s = 0; s < C::NS; ++s)
                     tma_load_5d(sQ + qb * C::Q_BYTES + s * C::Q_SLAB, &tm_q, q_full + qb, s * 64, c0, r0, hn, hb);
@@ -167,14 +174,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     NA2D_TR(1, 0, n);
                     if (!lt.acquire(k_empty + sk, ((n / NSTK) & 1) ^ 1, wctx)) break;
                     NA2D_TR(1, 1, n);
-                    lt.arm(2 + sk, k_full + sk, (n / NSTK) & 1, (uint32_t)C::NS * C::NK * C::ROWB);
+                    lt.arm(k_full + sk, (n / NSTK) & 1, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
                         tma_load_5d(sK + sk * C::K_BYTES + s * C::K_SLAB, &tm_k, k_full + sk, s * 64, box_c0,
                                     box_r0 + c * C::RC, hn, hb);
                     if (!lt.acquire(v_empty + sv, ((n / NSTV) & 1) ^ 1, wctx)) break;
                     NA2D_TR(1, 2, n);
-                    lt.arm(4 + sv, v_full + sv, (n / NSTV) & 1, (uint32_t)C::NS * C::NK * C::ROWB);
+                    lt.arm(v_full + sv, (n / NSTV) & 1, (uint32_t)C::NS * C::NK * C::ROWB);
 #pragma unroll
                     for (int s = 0; s < C::NS; ++s)
                         tma_load_5d(sV + sv * C::V_BYTES + s * C::KV_SLAB, &tm_v, v_full + sv, s * 64, box_c0,
@@ -190,8 +197,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         constexpr uint32_t idesc_s = umma_idesc(TM, C::NKP, IsBf16<DT>::value, IsBf16<DT>::value, false, false);
         constexpr uint32_t idesc_o = umma_idesc(TM, D, IsBf16<DT>::value, IsBf16<DT>::value, false, true);
         constexpr uint32_t hi = smem_desc_hi(C::ATOM, C::SWZ);
-        for (uint32_t n = 0; n < total_units; ++n) {
-            const uint32_t i = n / C::NCH, c = n % C::NCH, sk = n % NSTK, sv = n % NSTV, qb = i % NQ, ob = i & 1;
+        // O buffer and phase of tile i
+        auto o_buf = [](uint32_t i) { return C::NOB == 2 ? (i & 1u) : 0u; };
+        auto o_par = [](uint32_t i) { return C::NOB == 2 ? ((i >> 1) & 1u) : (i & 1u); };
+        // S(n) = Q K_c^T into S buffer n & 1
+        auto scores = [&](uint32_t n) {
+            const uint32_t i = n / C::NCH, c = n % C::NCH, sk = n % NSTK, qb = i % NQ;
             if (lane == 0) NA2D_TR(2, 0, n);
             if (c == 0) mbar_wait(q_full + qb, (i / NQ) & 1, wctx, kErrLoadWait);
             mbar_wait(k_full + sk, (n / NSTK) & 1, wctx, kErrLoadWait);
@@ -199,30 +210,36 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             tc_fence_after();
             const uint32_t q_lo = smem_desc_lo(smem_u32(sQ + qb * C::Q_BYTES), 16);
             const uint32_t k_lo = smem_desc_lo(smem_u32(sK + sk * C::K_BYTES), 16);
+            const uint32_t t_s = tmem_base + C::TMEM_S + (n & 1) * C::TMEM_SSTRIDE;
             if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     constexpr int kPerSlab = C::SLAB_C / 16;
                     const int slab = kk / kPerSlab, in_slab = kk % kPerSlab;
-                    umma_ss(tmem_base + C::TMEM_S, desc64(hi, q_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
+                    umma_ss(t_s, desc64(hi, q_lo + ((slab * C::Q_SLAB) >> 4) + 2 * in_slab),
                             desc64(hi, k_lo + ((slab * C::K_SLAB) >> 4) + 2 * in_slab), idesc_s, kk > 0);
                 }
-                umma_commit(s_full);
+                umma_commit(s_full + (n & 1));
                 umma_commit(k_empty + sk);
                 if (c == C::NCH - 1) umma_commit(q_empty + qb);           // the tile's Q buffer is free
             }
             __syncwarp();
             if (lane == 0) NA2D_TR(2, 2, n);
+        };
+        // O (+)= P(n) V_c, P read from S buffer n & 1
+        auto outputs = [&](uint32_t n) {
+            const uint32_t i = n / C::NCH, c = n % C::NCH, sv = n % NSTV, ob = o_buf(i);
             mbar_wait(v_full + sv, (n / NSTV) & 1, wctx, kErrLoadWait);
-            mbar_wait(p_full, n & 1, wctx, kErrMmaWait);
+            mbar_wait(p_full + (n & 1), (n >> 1) & 1, wctx, kErrMmaWait);
             if (lane == 0) NA2D_TR(2, 3, n);
-            if (c == 0) mbar_wait(o_free + ob, ((i >> 1) & 1) ^ 1, wctx, kErrMmaWait);
+            if (c == 0) mbar_wait(o_free + ob, o_par(i) ^ 1, wctx, kErrMmaWait);   // the tile before has been read out
             tc_fence_after();
             const uint32_t v_lo = smem_desc_lo(smem_u32(sV + sv * C::V_BYTES), C::KV_SLAB);
+            const uint32_t t_p = tmem_base + C::TMEM_S + (n & 1) * C::TMEM_SSTRIDE;
             if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < C::NKP / 16; ++kk) {
-                    umma_ts(tmem_base + C::TMEM_O0 + ob * C::TMEM_OSTRIDE, tmem_base + C::TMEM_S + 8 * kk,
+                    umma_ts(tmem_base + C::TMEM_O0 + ob * C::TMEM_OSTRIDE, t_p + 8 * kk,
                             desc64(hi, v_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, (c > 0) || (kk > 0));
                 }
                 umma_commit(v_empty + sv);
@@ -231,6 +248,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             }
             __syncwarp();
             if (lane == 0) NA2D_TR(2, 4, n);
+        };
+        // On the pipe: S(0) S(1) | PV(0) S(2) | PV(1) S(3) | ...  S(n + 2) goes into the buffer PV(n)
+        // has just read; the pipe runs its MMAs in the order they were issued.
+        if (total_units > 0) scores(0);
+        if (total_units > 1) scores(1);
+        for (uint32_t n = 0; n < total_units; ++n) {
+            outputs(n);
+            if (n + 2 < total_units) scores(n + 2);
         }
     } else if (warp >= 10) {
         reg_dec<kRegsDonor>();                 // spare warps of the data-movement group
@@ -247,13 +272,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         uint32_t pend_tile = 0;
         float pend_max = 0.f, pend_sum = 1.f;
         size_t pend_qi = 0;
-        int pend_hn = 0, pend_hb = 0, pend_r0 = 0, pend_c0 = 0;
+        int pend_bn = 0, pend_r0 = 0, pend_c0 = 0;
 
         auto epilogue = [&]() {
-            const uint32_t ob = pend_tile & 1;
+            const uint32_t ob = C::NOB == 2 ? (pend_tile & 1u) : 0u;
             bar_sync(1 + quarter, 64);                                       // partner's row sum is in x_sum
             const float total = pend_sum + x_sum[((pend_tile & 1) * 2 + (half ^ 1)) * 128 + row];
-            mbar_wait(o_full + ob, (pend_tile >> 1) & 1, wctx, kErrMmaWait);
+            mbar_wait(o_full + ob, C::NOB == 2 ? ((pend_tile >> 1) & 1u) : (pend_tile & 1u), wctx, kErrMmaWait);
             tc_fence_after();
             const float inv = 1.f / total;
             uint32_t acc[DH];
@@ -265,16 +290,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(o_free + ob);                         // O is in registers
+            int hn, hb;
+            split_unit(pend_bn, g, hn, hb);
             stage_and_store<DT, DH>(&tm_o, sOut + warp * OutStage<DH>::BYTES, acc, inv, half * DH, pend_c0,
-                                    pend_r0 + quarter * (32 / TW), pend_hn, pend_hb, lane);
+                                    pend_r0 + quarter * (32 / TW), hn, hb, lane);
             if (pend_valid && half == 0) lse[pend_qi] = (pend_max + log2f(total)) * kLn2;
             pend = false;
         };
 
         uint32_t n = 0;
         for (int i = 0; i < n_my; ++i) {
-            int bn, hn, hb, r0, c0;
-            decode(i, bn, hn, hb, r0, c0);
+            int bn, r0, c0;
+            decode(i, bn, r0, c0);
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
             const int qr_raw = r0 + (row / TW), qc_raw = c0 + (row % TW);
@@ -284,7 +311,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const int wc = na2d_ws(qc, g.W, KS) - box_c0;                            // in [0, TW)
             const int wr_lo = __shfl_sync(0xffffffffu, wr, 0);
             const int wr_hi = __shfl_sync(0xffffffffu, wr, 31);
-            const uint32_t o_addr = tmem_lane + C::TMEM_O0 + (i & 1) * C::TMEM_OSTRIDE + half * DH;
+            const uint32_t o_addr = tmem_lane + C::TMEM_O0 + (C::NOB == 2 ? (i & 1) : 0) * C::TMEM_OSTRIDE + half * DH;
             float run_max = -CUDART_INF_F, run_sum = 0.f;        // run_sum: this half's columns only
 
             // One chunk.  The warp's queries can only see a contiguous range of the chunk's columns
@@ -296,14 +323,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 constexpr int kRows = (32 / TW - 1 + KS) < C::RC ? (32 / TW - 1 + KS) : C::RC;
                 constexpr int kBlocks = (kRows * C::HW - 1) / 16 + 2;
                 constexpr int NACT = (kBlocks + 1) / 2 < NBH ? (kBlocks + 1) / 2 : NBH;
-                const uint32_t s_addr = tmem_lane + C::TMEM_S;
+                const uint32_t s_addr = tmem_lane + C::TMEM_S + (n & 1) * C::TMEM_SSTRIDE;
                 const int row_off = ch * C::RC;
                 const int j_lo = max(wr_lo - row_off, 0) * C::HW;
                 const int j_hi = min(min(wr_hi + KS - row_off, C::RC) * C::HW, C::NK);       // exclusive
                 const int b_hi = (max(j_hi, 0) + 15) >> 4;                                   // blocks [j_lo/16, b_hi)
                 const int bi_lo = ((j_lo >> 4) - half + 1) >> 1;                             // first own block in range
                 if (tid == 0) NA2D_TR(3, 0, n);
-                mbar_wait(s_full, n & 1, wctx, kErrMmaWait);
+                mbar_wait(s_full + (n & 1), (n >> 1) & 1, wctx, kErrMmaWait);
                 if (tid == 0) NA2D_TR(3, 1, n);
                 tc_fence_after();
 
@@ -405,7 +432,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_full);
+                if (lane == 0) mbar_arrive(p_full + (n & 1));
                 if (tid == 0) NA2D_TR(3, 4, n);
             };
 
@@ -417,8 +444,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             x_sum[((i & 1) * 2 + half) * 128 + row] = run_sum;
             pend = true;
             pend_tile = (uint32_t)i;
-            pend_hn = hn;
-            pend_hb = hb;
+            pend_bn = bn;
             pend_r0 = r0;
             pend_c0 = c0;
             pend_valid = q_valid;

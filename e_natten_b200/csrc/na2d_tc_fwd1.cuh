@@ -58,14 +58,13 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     uint64_t* kv_full = bars + 8;            // [4]  TMA -> MMA: K_A, K_B, V_A, V_B
     uint64_t* kv_empty = bars + 12;          // [4]  MMA (commit) -> TMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-    const WaitCtx wctx{abort_flag, err_word, kWaitLimitNs};
+    const WaitCtx wctx{reinterpret_cast<WaitState*>(bars + 17)};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
     if (tid == 0) {
-        *abort_flag = 0;
+        wait_state_init(wctx.st, err_word, kWaitLimitNs);
         mbar_init(q_full, 1);
         mbar_init(q_empty, 1);
         mbar_init(o_full, 1);
@@ -104,16 +103,15 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // my i-th tile: unit bn = head hn of batch hb, first row r0, first column c0
-    auto decode = [&](int i, int& bn, int& hn, int& hb, int& r0, int& c0) {
+    // my i-th tile: unit bn (head bn % N of batch bn / N, split where a TMA coordinate needs it),
+    // first row r0, first column c0
+    auto decode = [&](int i, int& bn, int& r0, int& c0) {
         int t = (int)blockIdx.x + i * (int)gridDim.x;
         const int tc = t % tiles_c;
         t /= tiles_c;
         r0 = (t % tiles_r) * TH;
         c0 = tc * TW;
         bn = t / tiles_r;
-        hb = bn / g.N;
-        hn = bn - hb * g.N;
     };
     // strip buffer of strip x of tile i: tile i uses (2i) % 3 and (2i + 1) % 3
     auto strip_col = [](int i, int x) { return ((2 * i + x) % 3) * C::TMEM_STRIP; };
@@ -126,16 +124,17 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         reg_dec<kDkvRegsCtl>();
         if (lane == 0) {
             const int j0 = warp == 8 ? 0 : 2;
-            LoadTracker<3> lt;                                          // slots: K_A / V_A, K_B / V_B, Q
+            LoadTracker lt(bars);
             for (int i = 0; i < n_my; ++i) {
-                int bn, hn, hb, r0, c0;
-                decode(i, bn, hn, hb, r0, c0);
+                int bn, r0, c0, hn, hb;
+                decode(i, bn, r0, c0);
+                split_unit(bn, g, hn, hb);
                 const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
                 const int box_c0 = na2d_ws(c0, g.W, KS);
                 const uint32_t par_free = (i & 1) ^ 1;
                 if (warp == 8) {
                     if (!lt.acquire(q_empty, par_free, wctx)) break;
-                    lt.arm(2, q_full, i & 1, (uint32_t)C::Q_BYTES);
+                    lt.arm(q_full, i & 1, (uint32_t)C::Q_BYTES);
 #pragma unroll
                     for (int sl = 0; sl < C::NS; ++sl) tma_load_5d(sQ + sl * C::Q_SLAB, &tm_q, q_full, sl * 64, c0, r0, hn, hb);
                 }
@@ -145,7 +144,7 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 for (int x = 0; x < 2; ++x) {
                     const int j = j0 + x;                               // K_A, K_B or V_A, V_B
                     if (!lt.acquire(kv_empty + j, par_free, wctx)) break;
-                    lt.arm(x, kv_full + j, i & 1, (uint32_t)C::NS * C::NK * C::ROWB);
+                    lt.arm(kv_full + j, i & 1, (uint32_t)C::NS * C::NK * C::ROWB);
                     uint8_t* dst = sKV + j * C::KV_BYTES;
 #pragma unroll
                     for (int sl = 0; sl < C::NS; ++sl) {
@@ -232,8 +231,9 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         uint8_t* stage = sOut + quarter * OutStage<32>::BYTES;
         constexpr int RPO = D / 32;                          // 32-channel rounds
         for (int i = 0; i < n_my; ++i) {
-            int bn, hn, hb, r0, c0;
-            decode(i, bn, hn, hb, r0, c0);
+            int bn, r0, c0, hn, hb;
+            decode(i, bn, r0, c0);
+            split_unit(bn, g, hn, hb);
             const uint32_t par = i & 1;
             const int qr = r0 + (row / TW), qc = c0 + (row % TW);
             mbar_wait(o_full, par, wctx, kErrMmaWait);            // also: the softmax warps' sums are written
@@ -272,8 +272,8 @@ fwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         constexpr unsigned long long kRepLo = C::REP_LO, kRepHi = C::REP_HI;   // bit r * HW for the ks window rows
 
         for (int i = 0; i < n_my; ++i) {
-            int bn, hn, hb, r0, c0;
-            decode(i, bn, hn, hb, r0, c0);
+            int bn, r0, c0;
+            decode(i, bn, r0, c0);
             const uint32_t par = i & 1;
             const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
             const int box_c0 = na2d_ws(c0, g.W, KS);
