@@ -382,13 +382,13 @@ def run_row_sharded(wl, dev, rank, world, steps, warmup):
     q, d_o = mk(), mk()
     ws.k_local.copy_(mk())                               # K / V are built in place, in the extended buffers
     ws.v_local.copy_(mk())
-    o, d_q = torch.empty_like(q), torch.empty_like(q)
+    o, d_q, d_k, d_v = (torch.empty_like(q) for _ in range(4))
     lse = torch.empty((B, N, sh.R, W), dtype=torch.float32, device=dev)
     delta = torch.empty_like(lse)
 
     def step():
         sharding.forward_band_into(ws, q, o, lse, ks)
-        return sharding.backward_band_into(ws, q, o, lse, d_o, d_q, delta, ks)
+        sharding.backward_band_into(ws, q, o, lse, d_o, d_q, d_k, d_v, delta, ks)
 
     for _ in range(max(warmup, 3)):
         step()
@@ -656,7 +656,7 @@ def main():
                 "halo_bytes_per_step_per_gpu": halo_bytes,
                 "value": 3.5 * flops_fwd(*c5[:6]) / (tn * 1e-3) / 1e12, "unit": "TFLOP/s", "scaling": "strong",
                 "exchange": "NCCL point-to-point: K/V halo rows received into the extended buffers while the interior "
-                            "rows' forward runs; fp32 dK/dV halo partials reduced after the backward"}
+                            "rows' forward runs; fp32 dK/dV halo partials exchanged while the interior key rows' dK/dV runs"}
     clocks = sampler.stop() if rank == 0 else None
 
     if rank != 0:

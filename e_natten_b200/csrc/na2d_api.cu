@@ -154,7 +154,10 @@ bool tma_compatible(const Tensor& t) {
     return true;
 }
 
-int make_problem(const na2d_args* a, Problem* out) {
+// `key_side`: the call is the key half of the backward, whose key band may be any part of the image
+// (each key sums over whichever local queries see it); the other calls need a key band that holds
+// every window of the query band.
+int make_problem(const na2d_args* a, Problem* out, bool key_side = false) {
     if (!a || a->struct_size < sizeof(na2d_args)) return NA2D_ERR_BAD_ARG;
     const int B = a->B, N = a->N, H = a->H, W = a->W, C = a->C, ks = a->kernel_size, dtype = a->dtype, path = a->path;
     if (B <= 0 || N <= 0 || H <= 0 || W <= 0 || C <= 0) return NA2D_ERR_BAD_ARG;
@@ -190,8 +193,10 @@ int make_problem(const na2d_args* a, Problem* out) {
         // (e_natten/pytorch.py:7-11 goes negative); here that is an error.
         if (g.Hg < ks || W < ks) return NA2D_ERR_WINDOW;
         // the key band must hold every window of the query band
-        if (na2d_ws(g.q_row0, g.Hg, ks) < g.kv_row0) return NA2D_ERR_WINDOW;
-        if (na2d_ws(g.q_row0 + g.Hq - 1, g.Hg, ks) + ks > g.kv_row0 + g.Hkv) return NA2D_ERR_WINDOW;
+        if (!key_side) {
+            if (na2d_ws(g.q_row0, g.Hg, ks) < g.kv_row0) return NA2D_ERR_WINDOW;
+            if (na2d_ws(g.q_row0 + g.Hq - 1, g.Hg, ks) + ks > g.kv_row0 + g.Hkv) return NA2D_ERR_WINDOW;
+        }
     }
     Problem& p = *out;
     p.q = resolve(a->q, B, N, g.Hq, W, C, one_d);
@@ -371,9 +376,9 @@ int run_backward_dkdv(const Problem& p) {
 
 // Validate, select the device, check it; then run `step`.
 template <typename F>
-int enter(const na2d_args* a, F&& step) {
+int enter(const na2d_args* a, F&& step, bool key_side = false) {
     Problem p;
-    int rc = make_problem(a, &p);
+    int rc = make_problem(a, &p, key_side);
     if (rc != NA2D_OK) return rc;
     DeviceScope scope(p.device);
     if (scope.err != cudaSuccess) return cuda_fail(scope.err, "cudaSetDevice");
@@ -563,7 +568,7 @@ int na2d_backward_dq_ex(const na2d_args* a) {
 int na2d_backward_dkdv_ex(const na2d_args* a) {
     if (!a || !a->q.ptr || !a->k.ptr || !a->v.ptr || !a->lse || !a->d_o.ptr || !a->delta || !a->d_k.ptr || !a->d_v.ptr)
         return NA2D_ERR_BAD_ARG;
-    return enter(a, [](const Problem& p) { return run_backward_dkdv(p); });
+    return enter(a, [](const Problem& p) { return run_backward_dkdv(p); }, /*key_side=*/true);
 }
 
 int na2d_backward_ex(const na2d_args* a) {

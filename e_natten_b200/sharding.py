@@ -24,10 +24,12 @@ Two ways to split the work over the GPUs of one box, one process per GPU:
     contiguous run per (batch, head) slab, while the forward of the *interior* query rows - those
     whose windows stay inside the rank's own rows - already runs; the two boundary strips of
     ``kernel_size // 2`` query rows follow when the halo has arrived.
-  - The backward computes dQ for the band and the partial dK / dV for all extended rows in fp32
+  - The backward computes dQ for the band, and dK / dV in up to three launches over parts of the
+    extended key rows: the interior key rows go straight into dK / dV; the two edge strips (halo
+    rows and the own rows the neighbours' queries also see) are partial sums and are kept in fp32
     (a partial sum can be much larger than the total, so it is not rounded to 16 bits before it
-    is added), sends the halo rows' partials to their owners and adds what arrives for its own
-    edge rows; the sum is rounded once.
+    is added); the halo rows' partials go to their owners while the interior launch runs, and
+    what arrives is added to the own edge rows and rounded once.
 
 The arithmetic is injected (``forward_fn`` / ``backward_fn``) so that the exchange logic can be
 exercised on CPU tensors in tests; by default it is the library's CUDA entry points.
@@ -132,6 +134,21 @@ class RowShardWorkspace:
 
     def matches(self, k: torch.Tensor) -> bool:
         return tuple(k.shape) == tuple(self.k_local.shape) and k.dtype == self._dtype and k.device == self.k_ext.device
+
+    def edge_buffers(self):
+        """fp32 buffers of the two edge strips of the key half (halo rows plus the own rows the
+        neighbours contribute to), [dK, dV] each, and the receive buffers of the neighbours'
+        partials; allocated on first use."""
+        if getattr(self, "_edges", None) is None:
+            sh = self.shard
+            B, N, _, W, C = self._shape
+            pd = _partial_dtype(self._dtype)
+            up, dn = _neighbours(sh)
+            n_up = up.bot if up is not None else 0
+            n_dn = dn.top if dn is not None else 0
+            mk = lambda rows: [torch.empty((B, N, rows, W, C), dtype=pd, device=self._device) for _ in range(2)] if rows > 0 else None
+            self._edges = {"top": mk(sh.top + n_up), "bot": mk(sh.bot + n_dn), "recv_up": mk(n_up), "recv_dn": mk(n_dn)}
+        return self._edges
 
     def partial_buffers(self):
         """(dk_ext, dv_ext, recv_up, recv_dn): fp32 (or the inputs' wider dtype), allocated on first use."""
@@ -266,17 +283,55 @@ def forward_band_into(ws: RowShardWorkspace, q, o, lse, kernel_size: int, group=
         lse[:, :, lo:hi].copy_(part)
 
 
-def backward_band_into(ws: RowShardWorkspace, q, o, lse, d_o, d_q, delta, kernel_size: int, group=None,
-                       scale: float = 1.0, path: str = "auto"):
-    """Backward of this rank's band: dQ into ``d_q``, the partial dK / dV of all extended rows in
-    fp32 into the workspace, then the halo reduction.  Returns (dK, dV) of the own rows."""
+def backward_band_into(ws: RowShardWorkspace, q, o, lse, d_o, d_q, d_k, d_v, delta, kernel_size: int, group=None,
+                       scale: float = 1.0, path: str = "auto") -> None:
+    """Backward of this rank's band into caller-owned ``d_q``, ``d_k``, ``d_v`` (B, N, R, W, C).
+
+    dQ comes from one launch over the band.  The key half runs in up to three launches over parts
+    of the extended key rows: the interior key rows - every query that sees them is local - go
+    straight into ``d_k`` / ``d_v`` in the tensors' dtype; the two edge strips (the halo rows this
+    rank computed for its neighbours, and its own rows that the neighbours' queries see as well) are
+    partial sums and go into small fp32 buffers.  The halo partials are sent to their owners, what
+    arrives is added to the own edge rows, and those are rounded once into ``d_k`` / ``d_v``."""
     sh = ws.shard
-    dk_ext, dv_ext, recv_up, recv_dn = ws.partial_buffers()
-    rows = sh.rows()
-    F.backward_dq_into(q, ws.k_ext, ws.v_ext, o, lse, d_o, d_q, delta, kernel_size, rows=rows, path=path, scale=scale)
-    F.backward_dkdv_into(q, ws.k_ext, ws.v_ext, lse, d_o, delta, dk_ext, dv_ext, kernel_size, rows=rows, path=path,
-                         scale=scale)
-    return reduce_dkdv_halo(dk_ext, dv_ext, sh, group, out_dtype=ws.k_ext.dtype, recv=(recv_up, recv_dn))
+    up, dn = _neighbours(sh)
+    top, bot, R = sh.top, sh.bot, sh.R
+    n_up = up.bot if up is not None else 0          # own first rows that rank - 1 also contributes to
+    n_dn = dn.top if dn is not None else 0
+    F.backward_dq_into(q, ws.k_ext, ws.v_ext, o, lse, d_o, d_q, delta, kernel_size, rows=sh.rows(), path=path, scale=scale)
+    edges = ws.edge_buffers()
+
+    def key_half(ext_lo, ext_hi, dk, dv):
+        rows = F.make_rows(sh.row0, R, sh.kv_row0 + ext_lo, ext_hi - ext_lo, sh.H)
+        F.backward_dkdv_into(q, ws.k_ext[:, :, ext_lo:ext_hi], ws.v_ext[:, :, ext_lo:ext_hi], lse, d_o, delta, dk, dv,
+                             kernel_size, rows=rows, path=path, scale=scale)
+
+    # edge strips first, so that their partials are on their way while the interior runs
+    if top + n_up > 0:
+        key_half(0, top + n_up, edges["top"][0], edges["top"][1])
+    if bot + n_dn > 0:
+        key_half(top + R - n_dn, sh.Hkv, edges["bot"][0], edges["bot"][1])
+    ops = []
+    for i in range(2):
+        if up is not None:
+            if top > 0:
+                ops += [dist.P2POp(dist.isend, s, _peer(group, sh.rank - 1), group) for s in _slabs(edges["top"][i], slice(0, top))]
+            if n_up > 0:
+                ops += [dist.P2POp(dist.irecv, s, _peer(group, sh.rank - 1), group) for s in _slabs(edges["recv_up"][i], slice(0, n_up))]
+        if dn is not None:
+            if bot > 0:
+                ops += [dist.P2POp(dist.isend, s, _peer(group, sh.rank + 1), group) for s in _slabs(edges["bot"][i], slice(n_dn, n_dn + bot))]
+            if n_dn > 0:
+                ops += [dist.P2POp(dist.irecv, s, _peer(group, sh.rank + 1), group) for s in _slabs(edges["recv_dn"][i], slice(0, n_dn))]
+    reqs = dist.batch_isend_irecv(ops) if ops else []
+    if R - n_up - n_dn > 0:
+        key_half(top + n_up, top + R - n_dn, d_k[:, :, n_up:R - n_dn], d_v[:, :, n_up:R - n_dn])
+    finish_exchange(reqs)
+    for i, out in enumerate((d_k, d_v)):
+        if n_up > 0:
+            out[:, :, :n_up] = edges["top"][i][:, :, top:] + edges["recv_up"][i]
+        if n_dn > 0:
+            out[:, :, R - n_dn:] = edges["bot"][i][:, :, :n_dn] + edges["recv_dn"][i]
 
 
 def _default_forward(q, k_ext, v_ext, ks, rows):
@@ -320,6 +375,14 @@ class RowShardedNatten2d(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         q, k_ext, v_ext, o, lse = ctx.saved_tensors
+        if ctx.backward_fn is None:               # the library's kernels: key half in interior + edge launches
+            d_o = F.as_kernel_input(grad_output)
+            d_q = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            d_k = torch.empty(q.shape, dtype=ctx.kv_dtype, device=q.device)
+            d_v = torch.empty(q.shape, dtype=ctx.kv_dtype, device=q.device)
+            delta = torch.empty(lse.shape, dtype=torch.float32, device=q.device)
+            backward_band_into(ctx.ws, F.as_kernel_input(q), o, lse, d_o, d_q, d_k, d_v, delta, ctx.kernel_size, ctx.group)
+            return d_q, d_k, d_v, None, None, None, None, None, None
         d_q, dk_ext, dv_ext = (ctx.backward_fn or _default_backward)(
             q, k_ext, v_ext, o, lse, grad_output, ctx.kernel_size, ctx.shard.rows())
         pd = _partial_dtype(ctx.kv_dtype)

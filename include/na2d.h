@@ -115,7 +115,8 @@ int na2d_backward_dq(const void* q, const void* k, const void* v, const void* o,
  * na2d_backward_dq on the same stream.  Replaces the atomic-add part of _attn_bwd_2d
  * (e_natten/triton.py:412-423): no atomics, every element is written exactly once, so no
  * pre-zeroing is needed.  With a row view, dK / dV cover the key band and hold the partial sums
- * over the local query band only. */
+ * over the local query band only; for this call the key band may be any rows of the image (it
+ * need not hold the query band's windows), so a caller can take the key rows in several calls. */
 int na2d_backward_dkdv(const void* q, const void* k, const void* v, const float* lse,
                        const void* d_o, const float* delta, void* d_k, void* d_v,
                        int B, int N, int H, int W, int C, int kernel_size, int dtype,
