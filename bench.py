@@ -71,14 +71,16 @@ def flops_fwd(B, N, H, W, C, ks):
 def algorithmic_bytes(B, N, H, W, C, esize):
     T = B * N * H * W * C * esize
     L = B * N * H * W * 4
-    return {"fwd": 4 * T + L, "dq": 6 * T + 2 * L, "dkdv": 6 * T + 2 * L, "bwd": 8 * T + L,
+    # per launch: forward reads q,k,v and writes o,lse; the dQ kernel reads q,k,v,dO,lse and writes dQ,delta;
+    # the dK/dV kernel reads q,k,v,dO,lse,delta and writes dK,dV.  "bwd" and "step" are the one-pass figures.
+    return {"fwd": 4 * T + L, "dq": 5 * T + 2 * L, "dkdv": 6 * T + 2 * L, "bwd": 8 * T + L,
             "step": 12 * T + 2 * L, "T": T, "L": L}
 
 
 # DRAM bytes (read + written) per launch of the three kernels on the headline workload, from an ncu
 # capture of that workload itself (dram__bytes_read.sum + dram__bytes_write.sum, one launch each).
-# None until such a capture has been taken.
-NCU_DRAM_BYTES = {"c2-256": {"na2d forward": None, "na2d backward dQ": None, "na2d backward dK/dV": None}}
+NCU_DRAM_BYTES = {"c2-256": {"na2d forward": 805445632 + 248020736, "na2d backward dQ": 1078204416 + 249562368,
+                             "na2d backward dK/dV": 1082870016 + 499711744}}
 NCU_TRAFFIC_SOURCE = "ncu capture of this workload (c2-256), one launch per kernel"
 
 

@@ -302,6 +302,29 @@ int run_forward(const Problem& p) {
     });
 }
 
+// The dO . o estimate of the row deltas, into p.delta (tensor path: head dim 32, 64 or 128, rows on
+// 16-byte boundaries).
+template <typename T, int LPP>
+int launch_delta_as(const Problem& p) {
+    const Na2dGeom& g = p.g;
+    const long long hw = (long long)g.Hq * g.W;
+    const long long per_image = (hw + na2d_delta::pixels_per_block<LPP>() - 1) / na2d_delta::pixels_per_block<LPP>();
+    if (hw > 0x7fffffffLL || per_image * g.BN > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
+    na2d_delta::delta_kernel<T, LPP><<<(unsigned)(per_image * g.BN), na2d_delta::kThreads, 0, p.st>>>(
+        (const T*)p.d_o.ptr, (const T*)p.o.ptr, p.delta, p.d_o.st, p.o.st, g, (unsigned)per_image);
+    return after_launch();
+}
+
+int launch_delta(const Problem& p) {
+    const bool bf = p.dtype == NA2D_BF16;
+    switch (p.g.C) {
+        case 32: return bf ? launch_delta_as<__nv_bfloat16, 4>(p) : launch_delta_as<__half, 4>(p);
+        case 64: return bf ? launch_delta_as<__nv_bfloat16, 8>(p) : launch_delta_as<__half, 8>(p);
+        case 128: return bf ? launch_delta_as<__nv_bfloat16, 16>(p) : launch_delta_as<__half, 16>(p);
+        default: return NA2D_ERR_UNSUPPORTED;
+    }
+}
+
 int run_backward_dq(const Problem& p) {
     const Na2dGeom& g = p.g;
     if (p.tensor) {
@@ -314,17 +337,7 @@ int run_backward_dq(const Problem& p) {
         // exact deltas.
         const float* delta_in = nullptr;
         if (g.ks >= 7 && p.o.ptr && p.d_q.ptr) {
-            const long long nq = (long long)g.BN * g.Hq * g.W;
-            const long long nb = (nq + na2d_delta::kWarps - 1) / na2d_delta::kWarps;
-            if (nb > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
-            const unsigned grid = (unsigned)nb;
-            if (p.dtype == NA2D_BF16)
-                na2d_delta::delta_kernel<__nv_bfloat16><<<grid, na2d_delta::kWarps * 32, 0, p.st>>>(
-                    (const __nv_bfloat16*)p.d_o.ptr, (const __nv_bfloat16*)p.o.ptr, p.delta, p.d_o.st, p.o.st, g);
-            else
-                na2d_delta::delta_kernel<__half><<<grid, na2d_delta::kWarps * 32, 0, p.st>>>(
-                    (const __half*)p.d_o.ptr, (const __half*)p.o.ptr, p.delta, p.d_o.st, p.o.st, g);
-            rc = after_launch();
+            rc = launch_delta(p);
             if (rc != NA2D_OK) return rc;
             delta_in = p.delta;
         }

@@ -6,8 +6,10 @@
 // needs to walk its key box once instead of twice: it forms dS from the estimate and corrects
 // the result exactly at the end (see na2d_tc_bwd.cuh).
 //
-// One warp per query pixel, lanes over channels; plain coalesced loads, an HBM-bound pass over
-// two tensors.
+// C / 8 lanes per query pixel, each lane one 16-byte piece of the two rows; a block covers
+// 256 / (C / 8) consecutive pixels of one (batch, head) image, so a warp's loads are whole rows
+// lying one after another.  An HBM-bound pass over two tensors: no division beyond one 32-bit
+// one per thread.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -17,7 +19,7 @@
 
 namespace na2d_delta {
 
-constexpr int kWarps = 8;
+constexpr int kThreads = 256;
 
 template <typename T> __device__ __forceinline__ float2 to_f2(uint32_t w);
 template <> __device__ __forceinline__ float2 to_f2<__nv_bfloat16>(uint32_t w) {
@@ -27,30 +29,44 @@ template <> __device__ __forceinline__ float2 to_f2<__half>(uint32_t w) {
     return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
 
-// C is a multiple of 2; every row starts on a 4-byte boundary.
 template <typename T>
-__global__ void __launch_bounds__(kWarps * 32)
+__device__ __forceinline__ float dot8(const uint4 a, const uint4 x, float acc) {
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 fa = to_f2<T>(aw[i]), fx = to_f2<T>(xw[i]);
+        acc = fmaf(fa.x, fx.x, acc);
+        acc = fmaf(fa.y, fx.y, acc);
+    }
+    return acc;
+}
+
+// Pixels of one image a block covers.
+template <int LPP> NA2D_HD constexpr int pixels_per_block() { return kThreads / LPP; }
+
+// LPP = C / 8 lanes per pixel (4, 8 or 16).  Every row starts on a 16-byte boundary.  The grid is
+// batch * heads * blocks_per_image blocks, an image's blocks next to one another.
+template <typename T, int LPP>
+__global__ void __launch_bounds__(kThreads)
 delta_kernel(const T* __restrict__ d_o, const T* __restrict__ o, float* __restrict__ delta, const Na2dStride s_do,
-             const Na2dStride s_o, const Na2dGeom g) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long n_query = (long long)g.BN * g.Hq * g.W;
-    const long long qi = (long long)blockIdx.x * kWarps + warp;
-    if (qi >= n_query) return;
-    const int w = (int)(qi % g.W);
-    const int h = (int)((qi / g.W) % g.Hq);
-    const long long bn = qi / ((long long)g.W * g.Hq);
-    const long long b = bn / g.N, n = bn - b * g.N;
-    const uint32_t* pg = reinterpret_cast<const uint32_t*>(d_o + b * s_do.b + n * s_do.n + h * s_do.h + w * s_do.w);
-    const uint32_t* po = reinterpret_cast<const uint32_t*>(o + b * s_o.b + n * s_o.n + h * s_o.h + w * s_o.w);
+             const Na2dStride s_o, const Na2dGeom g, const unsigned blocks_per_image) {
+    const unsigned hw = (unsigned)g.Hq * (unsigned)g.W;
+    const unsigned bn = blockIdx.x / blocks_per_image;
+    const unsigned pix = (blockIdx.x - bn * blocks_per_image) * pixels_per_block<LPP>() + threadIdx.x / LPP;
+    const unsigned part = threadIdx.x % LPP;
     float acc = 0.f;
-    for (int c2 = lane; c2 < g.C / 2; c2 += 32) {
-        const float2 a = to_f2<T>(pg[c2]), x = to_f2<T>(po[c2]);
-        acc = fmaf(a.x, x.x, acc);
-        acc = fmaf(a.y, x.y, acc);
+    if (pix < hw) {
+        const unsigned h = pix / (unsigned)g.W, w = pix - h * (unsigned)g.W;
+        const unsigned b = bn / (unsigned)g.N, n = bn - b * (unsigned)g.N;
+        const T* pg = d_o + b * s_do.b + n * s_do.n + h * s_do.h + w * s_do.w;
+        const T* po = o + b * s_o.b + n * s_o.n + h * s_o.h + w * s_o.w;
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(pg) + part);
+        const uint4 x = __ldg(reinterpret_cast<const uint4*>(po) + part);
+        acc = dot8<T>(a, x, 0.f);
     }
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
-    if (lane == 0) delta[qi] = acc;
+    for (int d = LPP / 2; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (part == 0 && pix < hw) delta[(long long)bn * hw + pix] = acc;
 }
 
 }  // namespace na2d_delta

@@ -58,6 +58,48 @@ def test_static_scratch_backward_matches_ordinary_backward_twice_in_a_row():
             assert torch.equal(a, b), f"{name}: same kernels, same inputs, yet different bits"
 
 
+def test_static_scratch_backward_allocates_nothing_once_warm_and_takes_a_row_view():
+    """After one warm-up call on the device (which makes the runtime load the library's device code,
+    the built-in array with it) a call changes neither the device's free memory nor what the
+    framework's allocator holds.  Run at the largest shape that fits (B4 N4 256x256) and, a second
+    time, on a row band of it through na2d_rows."""
+    B, N, H, W, Cd, ks, dtype = 4, 4, 256, 256, 32, 5, torch.bfloat16
+    assert B * N * H * W == 1 << 20
+    q, k, v, d_o = (torch.randn((B, N, H, W, Cd), device=DEV).mul(0.5).to(dtype) for _ in range(4))
+    o, lse = na.natten2d_forward(q, k, v, ks)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    outs = [torch.empty_like(q) for _ in range(3)]
+
+    def call(rows, qq, kk, vv, oo, ll, gg, dq, dk, dv):
+        b, n, h, w, c = qq.shape
+        return _lib.lib.na2d_backward_static_scratch(_p(qq), _p(kk), _p(vv), _p(oo), _p(ll), _p(gg), _p(dq), _p(dk), _p(dv),
+                                                     b, n, h, w, c, ks, _DTYPES[dtype], rows, _lib.PATH_AUTO, 0, st)
+
+    _lib.check(call(None, q, k, v, o, lse, d_o, *outs))              # warm-up: first use of the array on this device
+    torch.cuda.synchronize()
+    free0, held0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    _lib.check(call(None, q, k, v, o, lse, d_o, *outs))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == held0
+    na.check_kernels(DEV)
+    ref = na.natten2d_backward(q, k, v, o, lse, d_o, ks)
+    for name, a, b in zip(("dq", "dk", "dv"), outs, ref):
+        assert torch.equal(a, b), f"{name} at the largest shape that fits"
+    # a row band of the same image: query rows [96, 160), the key rows their windows reach
+    a0, a1 = 96, 160
+    kv0 = na.get_window_start(a0, H, ks)
+    kv1 = na.get_window_start(a1 - 1, H, ks) + ks
+    rows = na.make_rows(a0, a1 - a0, kv0, kv1 - kv0, H)
+    qb, ob, lb, gb = (t[:, :, a0:a1].contiguous() for t in (q, o, lse, d_o))
+    kb, vb = k[:, :, kv0:kv1].contiguous(), v[:, :, kv0:kv1].contiguous()
+    got = [torch.empty_like(qb), torch.empty_like(kb), torch.empty_like(vb)]
+    _lib.check(call(C.byref(rows), qb, kb, vb, ob, lb, gb, *got))
+    na.check_kernels(DEV)
+    want = na.natten2d_backward(qb, kb, vb, ob, lb, gb, ks, rows=rows)
+    for name, a, b in zip(("dq", "dk", "dv"), got, want):
+        assert torch.equal(a, b), f"{name} under a row view"
+
+
 def test_static_scratch_backward_refuses_what_does_not_fit():
     limit = 1 << 20
     B, N, H, W, Cd = 1, 1, 1032, 1024, 32                       # 1032*1024 > 2**20 row deltas
