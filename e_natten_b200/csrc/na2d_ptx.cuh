@@ -180,6 +180,16 @@ __device__ __forceinline__ void tma_load_5d(void* dst, const void* tmap, uint64_
         : "memory");
 }
 
+// The same box brought into L2 only: nothing is written to shared memory and nothing signals
+// completion.  A producer issues it for a box it cannot load yet (its shared-memory buffer is
+// still being read), so that the load proper finds the data in L2.  Same coordinate rules.
+__device__ __forceinline__ void tma_prefetch_5d(const void* tmap, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];"
+        ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
 // 5-D tiled store shared -> global (bulk async-group completion).  Pixels of the box that lie
 // outside the tensor are not written.  Coordinates must not be negative; c0 as for loads.
 __device__ __forceinline__ void tma_store_5d(const void* tmap, uint32_t smem_src, int c0, int c1, int c2, int c3,

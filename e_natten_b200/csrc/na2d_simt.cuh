@@ -228,7 +228,7 @@ fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict
 // when it was stored (the reference's backward does not read o either, e_natten/triton.py:522).
 // d_q may be null: then only delta is produced.
 template <typename T, int CPL>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, 2)
 dq_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const float* __restrict__ lse,
           const T* __restrict__ d_o, T* __restrict__ d_q, float* __restrict__ delta, const Na2dStride sq,
           const Na2dStride sk, const Na2dStride sv, const Na2dStride sg, const Na2dStride sdq, const Na2dGeom g) {
@@ -297,7 +297,7 @@ __device__ __forceinline__ Inverse inverse_neighbourhood(int key_row_global, int
 // One warp per key pixel of the key band; sums over the queries of the local query band whose
 // window holds the key (the inverse neighbourhood, a product of two index ranges), 32 at a time.
 template <typename T, int CPL>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, 2)
 dkdv_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const float* __restrict__ lse,
             const T* __restrict__ d_o, const float* __restrict__ delta, void* __restrict__ d_k, void* __restrict__ d_v,
             const int f32_out, const Na2dStride sq, const Na2dStride sk, const Na2dStride sv, const Na2dStride sg,

@@ -12,9 +12,10 @@
 //
 // Tensor memory holds two chunk stages (S^T, dP^T of 64 columns each) next to the dV and dK
 // accumulators, so the score MMAs of one chunk run while the softmax warps work on the previous
-// one.  Sixteen warps: 0-3 and 4-7 are two softmax groups that take alternate chunks (a warp owns
-// the 32 keys of its lane quarter), 8 TMA producer of the Q / dO chunk ring, 11 TMA producer of the
-// K, V tile, 9 issues the score MMAs, 10 the output MMAs, 12-15 epilogue (dV, dK rows -> staging -> TMA store), which
+// one.  Sixteen warps: 0-7 softmax (warps w and w + 4 own the same 32 keys of a lane quarter and split
+// the 8-column blocks of every chunk between them), 8 TMA producer of the Q / dO chunk ring, 11 TMA
+// producer of the K, V tile, 9 issues the score MMAs, 10 the output MMAs, 12-15 epilogue (dV, dK rows ->
+// staging -> TMA store), which
 // overlaps the next tile.  dK and dV accumulate in tensor memory over all chunks of a tile; no
 // atomics.
 #pragma once
@@ -102,7 +103,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         mbar_init(acc_free, 4);
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full + i, 1);
-            mbar_init(p_full + i, 4);
+            mbar_init(p_full + i, 8);
             mbar_init(st_free + i, 1);
         }
         for (int i = 0; i < 4; ++i) {
@@ -298,6 +299,17 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     tma_load_5d(sV + s * C::Q_SLAB, &tm_v, kv_full, s * 64, t.kc0, t.kr0, t.hn, t.hb);
                 }
                 ++it;
+                // The single K, V buffer is only free again after this tile's last score MMAs, and a
+                // load from HBM issued then is what the next tile would wait for: bring the next
+                // tile's K, V into L2 now.
+                if (i + 1 < n_my) {
+                    const TileGeo tn = tile_geo(i + 1);
+#pragma unroll
+                    for (int s = 0; s < C::NS; ++s) {
+                        tma_prefetch_5d(&tm_k, s * 64, tn.kc0, tn.kr0, tn.hn, tn.hb);
+                        tma_prefetch_5d(&tm_v, s * 64, tn.kc0, tn.kr0, tn.hn, tn.hb);
+                    }
+                }
             }
             lt.drain(wctx);
         }
@@ -361,21 +373,52 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         if (lane == 0) bulk_wait<0>();                       // the staging buffer has been read, the rows written
     } else {
         // ------------------------------------------------------------------ softmax groups
+        // Both groups work on every chunk: warps w and w + 4 own the same 32 keys (tensor-memory
+        // lanes) and take alternate 8-column blocks of the warp's active range, so a chunk's S^T and
+        // dP^T spend half as long in registers before the output MMAs may start - that time is part
+        // of the chain that bounds the kernel (score MMAs -> this -> output MMAs -> stage free).
         reg_inc<kDkvRegsSoftmax>();
         const int quarter = warp & 3, group = warp >> 2;
         const int row = quarter * 32 + lane;                 // key of the tile = tensor-memory lane
         const int gtid = quarter * 32 + lane;                // 0..127 inside the group
-        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + group * C::TMEM_STAGE;
+        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         // a warp's 32 / TW key rows are seen from at most that many + 2 ks - 2 query rows
         constexpr int kRows = (32 / TW - 1 + 2 * KS - 1) < C::RC ? (32 / TW - 1 + 2 * KS - 1) : C::RC;
         constexpr int kBlocks = (kRows * C::HW - 1) / 8 + 2;
-        constexpr int NACT = kBlocks < C::NB8 ? kBlocks : C::NB8;   // 8-column blocks a warp can have in range
+        constexpr int NACT = kBlocks < C::NB8 ? kBlocks : C::NB8;   // 8-column blocks a warp pair can have in range
+        constexpr int NOWN = (NACT + 1) / 2;                        // of which one warp takes at most
         constexpr unsigned long long kRowRep = C::ROW_REP;          // bit r * HW set for every chunk row r
 
+        // lse and delta of this thread's query of chunk (rc, cc) of tile t (zero outside the band); the
+        // values are fetched one chunk ahead, so that their latency runs under the wait for the
+        // chunk's scores instead of before it
+        auto fetch = [&](const TileGeo& t, int rc, int cc, float& l2, float& dl) {
+            l2 = 0.f;
+            dl = 0.f;
+            if (gtid < C::NK) {
+                const int br = rc * C::RC + gtid / C::HW, qc = t.qb_c0 + cc * C::HW + gtid % C::HW;
+                if (br < t.n_rows && qc < g.W) {
+                    const size_t qi = (static_cast<size_t>(t.bn) * g.Hq + (t.q_local_r0 + br)) * g.W + qc;
+                    l2 = lse[qi];
+                    dl = delta[qi];
+                }
+            }
+        };
+        // first tile with chunks at or after i
+        auto next_tile = [&](int i, TileGeo& t) {
+            for (; i < n_my; ++i) {
+                t = tile_geo(i);
+                if (t.n_ch > 0) break;
+            }
+            return i;
+        };
+
         uint32_t n = 0;
-        for (int i = 0; i < n_my; ++i) {
-            const TileGeo t = tile_geo(i);
-            if (t.n_ch == 0) continue;
+        TileGeo t;
+        int i = next_tile(0, t);
+        float pre_l2 = 0.f, pre_dl = 0.f;
+        if (i < n_my) fetch(t, 0, 0, pre_l2, pre_dl);
+        while (i < n_my) {
             const int kr = min(t.kr0 + (row / TW), g.Hkv - 1), kc = min(t.kc0 + (row % TW), g.W - 1);
             // the queries that see this thread's key: box rows [row_lo, row_hi), box columns [col_lo, col_hi)
             const int kg = g.kv_row0 + kr;
@@ -385,26 +428,22 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
             const int col_hi = na2d_bwe(kc, g.W, KS) - t.qb_c0;
             const int wrow_lo = __shfl_sync(0xffffffffu, row_lo, 0);
             const int wrow_hi = __shfl_sync(0xffffffffu, row_hi, 31);
+            TileGeo t_next = t;
+            int i_next = n_my;
 
-            for (int ch = 0; ch < t.n_ch; ++ch, ++n) {
-                if ((n & 1u) != (uint32_t)group) continue;  // the other group's chunk
-                const uint32_t k = n >> 1;                  // this group's chunk counter
-                const int rc = ch / t.n_cc, cc = ch - rc * t.n_cc;
-                const int r_off = rc * C::RC, c_off = cc * C::HW;
+            for (int ch = 0, rc = 0, cc = 0; ch < t.n_ch; ++ch, ++n) {
+                const uint32_t stage = n & 1u, k = n >> 1;  // tensor-memory stage and its use counter
+                const uint32_t t_stage = tmem_lane + stage * C::TMEM_STAGE;
+                const int r_off = rc * C::RC, c_off = cc * C::HW;       // chunk ch = rc * n_cc + cc
                 if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 0, n);
-                float* x_lse = s_x + ((group * 2 + (k & 1)) * 2) * 64;
+                // each group keeps its own copy of the chunk's lse * log2(e) and delta (two buffers: a
+                // warp may be one chunk ahead of the others of its group, the barrier below keeps it
+                // from two)
+                float* x_lse = s_x + ((group * 2 + stage) * 2) * 64;
                 float* x_delta = x_lse + 64;
-                // lse * log2(e) and delta of the chunk's queries -> shared memory (zero outside the band)
                 if (gtid < C::NK) {
-                    const int br = r_off + gtid / C::HW, qc = t.qb_c0 + c_off + gtid % C::HW;
-                    float l2 = 0.f, dl = 0.f;
-                    if (br < t.n_rows && qc < g.W) {
-                        const size_t qi = (static_cast<size_t>(t.bn) * g.Hq + (t.q_local_r0 + br)) * g.W + qc;
-                        l2 = lse[qi] * kLog2e;
-                        dl = delta[qi];
-                    }
-                    x_lse[gtid] = l2;
-                    x_delta[gtid] = dl;
+                    x_lse[gtid] = pre_l2 * kLog2e;
+                    x_delta[gtid] = pre_dl;
                 }
                 // the warp's keys are seen from chunk rows [ra, rb): its active column range
                 const int ra = max(wrow_lo - r_off, 0), rb = min(wrow_hi - r_off, C::RC);
@@ -416,43 +455,63 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 const int cl = max(col_lo - c_off, 0), chi = min(col_hi - c_off, C::HW);
                 const int seg_len = chi - cl;
                 const uint32_t seg = seg_len > 0 ? ((1u << seg_len) - 1u) : 0u;
-                bar_sync(5 + group, 128);                                   // lse / delta are in place
-                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 1, n);
-
-                mbar_wait(s_full + group, k & 1, wctx, kErrMmaWait);
-                tc_fence_after();
-                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 2, n);
-                uint32_t s[NACT][8], dp[NACT][8];
-#pragma unroll
-                for (int a = 0; a < NACT; ++a) {
-                    const int blk = b_lo + a;
-                    if (blk < b_hi) {                                       // warp-uniform
-                        tmem_ld_32x8(tmem_lane + C::TMEM_ST + 8 * blk, s[a]);
-                        tmem_ld_32x8(tmem_lane + C::TMEM_DPT + 8 * blk, dp[a]);
-                    }
-                }
                 // validity of the chunk's (at most 64) columns for this thread's key, one bit each:
                 // its column segment repeated in every chunk row, cut to its row range
-                uint32_t vmask[NACT];
+                unsigned long long m64 = 0ull;
                 {
                     const int ta = max(row_lo - r_off, 0), tb = min(row_hi - r_off, C::RC);
                     const unsigned long long rows_hi = tb * C::HW >= 64 ? ~0ull : ((1ull << (max(tb, 0) * C::HW)) - 1ull);
                     const unsigned long long rows_lo = (1ull << (ta * C::HW)) - 1ull;       // ta * HW < 64
-                    const unsigned long long m64 = tb > ta ? (((kRowRep * seg) << cl) & rows_hi & ~rows_lo) : 0ull;
+                    if (tb > ta) m64 = ((kRowRep * seg) << cl) & rows_hi & ~rows_lo;
+                }
+                bar_sync(5 + group, 128);                                   // lse / delta are in place
+                if (++cc == t.n_cc) {
+                    cc = 0;
+                    ++rc;
+                }
+                if (ch + 1 < t.n_ch) {
+                    fetch(t, rc, cc, pre_l2, pre_dl);
+                } else {
+                    i_next = next_tile(i + 1, t_next);
+                    if (i_next < n_my) fetch(t_next, 0, 0, pre_l2, pre_dl);
+                }
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 1, n);
+
+                mbar_wait(s_full + stage, k & 1, wctx, kErrMmaWait);
+                tc_fence_after();
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 2, n);
+                uint32_t s[NOWN][8], dp[NOWN][8];
 #pragma unroll
-                    for (int a = 0; a < NACT; ++a) {
-                        const int blk = b_lo + a;
-                        vmask[a] = (blk < b_hi) ? (static_cast<uint32_t>(m64 >> (8 * blk)) & 0xffu) : 0u;
+                for (int a = 0; a < NOWN; ++a) {
+                    const int blk = b_lo + 2 * a + group;
+                    if (blk < b_hi) {                                       // warp-uniform
+                        tmem_ld_32x8(t_stage + C::TMEM_ST + 8 * blk, s[a]);
+                        tmem_ld_32x8(t_stage + C::TMEM_DPT + 8 * blk, dp[a]);
                     }
                 }
                 tmem_ld_wait();
+                // The 16-bit operands go over S^T / dP^T, a block's over other blocks' columns: the
+                // partner warp must have its blocks in registers too before either of them writes.
+                bar_sync(1 + quarter, 64);
                 if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 3, n);
-                // every S^T / dP^T block of this warp's lanes is in registers: the 16-bit operands
-                // may be written over them
+                {   // blocks outside the active range hold zeros (this warp: every other one of them)
+                    const uint32_t z[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                for (int a = 0; a < NACT; ++a) {
-                    const int blk = b_lo + a;
+                    for (int blk = 0; blk < C::NB8; ++blk) {
+                        const bool in_range = blk >= b_lo && blk < b_lo + NACT && blk < b_hi;
+                        if (!in_range && ((blk & 1) == group)) {
+                            tmem_st_32x4(t_stage + C::TMEM_PT + 4 * blk, z);
+                            tmem_st_32x4(t_stage + C::TMEM_DST + 4 * blk, z);
+                            if (SPLIT) tmem_st_32x4(t_stage + C::TMEM_RES + 4 * blk, z);
+                        }
+                    }
+                }
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 6, n);
+#pragma unroll
+                for (int a = 0; a < NOWN; ++a) {
+                    const int blk = b_lo + 2 * a + group;
                     if (blk < b_hi) {
+                        const uint32_t vmask = static_cast<uint32_t>(m64 >> (8 * blk)) & 0xffu;
                         float l2[8], dl[8];
 #pragma unroll
                         for (int v4 = 0; v4 < 2; ++v4) {
@@ -469,7 +528,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                             for (int h = 0; h < 2; ++h) {
                                 const int e = 2 * e2 + h;
                                 const float pe = fast_exp2(fmaf(__uint_as_float(s[a][e]), g.sl2, -l2[e]));
-                                const bool ok = (vmask[a] >> e) & 1u;      // select, never multiply by zero
+                                const bool ok = (vmask >> e) & 1u;         // select, never multiply by zero
                                 p[h] = ok ? pe : 0.f;
                                 ds[h] = ok ? pe * (__uint_as_float(dp[a][e]) - dl[e]) : 0.f;
                             }
@@ -477,28 +536,20 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                             wd[e2] = pack2<DT>(ds[0], ds[1]);
                             wr2[e2] = SPLIT ? pack2_residual_bf16(ds[0], ds[1], wd[e2]) : 0u;
                         }
-                        tmem_st_32x4(tmem_lane + C::TMEM_PT + 4 * blk, wp);
-                        tmem_st_32x4(tmem_lane + C::TMEM_DST + 4 * blk, wd);
-                        if (SPLIT) tmem_st_32x4(tmem_lane + C::TMEM_RES + 4 * blk, wr2);
+                        tmem_st_32x4(t_stage + C::TMEM_PT + 4 * blk, wp);
+                        tmem_st_32x4(t_stage + C::TMEM_DST + 4 * blk, wd);
+                        if (SPLIT) tmem_st_32x4(t_stage + C::TMEM_RES + 4 * blk, wr2);
                     }
                 }
-                {   // blocks outside the range hold zeros
-                    const uint32_t z[4] = {0u, 0u, 0u, 0u};
-                    for (int blk = 0; blk < C::NB8; ++blk) {
-                        const bool in_range = blk >= b_lo && blk < b_lo + NACT && blk < b_hi;
-                        if (!in_range) {
-                            tmem_st_32x4(tmem_lane + C::TMEM_PT + 4 * blk, z);
-                            tmem_st_32x4(tmem_lane + C::TMEM_DST + 4 * blk, z);
-                            if (SPLIT) tmem_st_32x4(tmem_lane + C::TMEM_RES + 4 * blk, z);
-                        }
-                    }
-                }
+                if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 4, n);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_full + group);
+                if (lane == 0) mbar_arrive(p_full + stage);
                 if (quarter == 0 && lane == 0) NA2D_TR(3 - 2 * group, 5, n);
             }
+            i = i_next;
+            t = t_next;
         }
     }
 

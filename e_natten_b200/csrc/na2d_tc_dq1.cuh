@@ -161,6 +161,21 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                         else tma_load_5d(dst + sl * C::KV_SLAB, &tm_k, st_full + slot[j], sl * 64, box_c0 + (j >> 1) * C::HW, box_r0, hn, hb);
                     }
                 }
+                // The buffers of the next tile's K_B and V_B are only free after this tile's dQ MMAs,
+                // and a load from HBM issued then is what the next tile's strip B would wait for:
+                // bring those two strips into L2 now.
+                if (i + 1 < n_my && lt.ok) {
+                    int bn2, r2, c2, hn2, hb2;
+                    decode(i + 1, bn2, r2, c2);
+                    split_unit(bn2, g, hn2, hb2);
+                    const int nr0 = na2d_ws(g.q_row0 + r2, g.Hg, KS) - g.kv_row0;
+                    const int nc0 = na2d_ws(c2, g.W, KS) + C::HW;
+#pragma unroll
+                    for (int sl = 0; sl < C::NS; ++sl) {
+                        tma_prefetch_5d(&tm_k, sl * 64, nc0, nr0, hn2, hb2);
+                        tma_prefetch_5d(&tm_v, sl * 64, nc0, nr0, hn2, hb2);
+                    }
+                }
             }
             lt.drain(wctx);
         }
@@ -181,10 +196,16 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const Slots s = slots_of(i);
             const int sk = x ? s.kb : s.ka, sv = x ? s.vb : s.va;
             const uint32_t par = i & 1;
+            if (x == 0 && lane == 0) NA2D_TR(0, 0, i);
             if (x == 0) mbar_wait(q_full, par, wctx, kErrLoadWait);
+            if (x == 0 && lane == 0) NA2D_TR(0, 1, i);
             mbar_wait(st_full + sk, par, wctx, kErrLoadWait);
+            if (x == 0 && lane == 0) NA2D_TR(0, 2, i);
             mbar_wait(st_full + sv, par, wctx, kErrLoadWait);
+            if (x == 0 && lane == 0) NA2D_TR(0, 3, i);
+            if (x == 1 && lane == 0) NA2D_TR(0, 4, i);
             if (x == 1) mbar_wait(dq_free, par ^ 1, wctx, kErrMmaWait);     // dQ of tile i - 1 sits over S_B
+            if (x == 1 && lane == 0) NA2D_TR(0, 5, i);
             tc_fence_after();
             const uint32_t k_lo = smem_desc_lo(strip_base + sk * C::KV_BYTES, 16);
             const uint32_t v_lo = smem_desc_lo(strip_base + sv * C::KV_BYTES, 16);
@@ -260,34 +281,41 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         constexpr int NACT = (kBlocks + 1) / 2 < NBH ? (kBlocks + 1) / 2 : NBH;
         constexpr unsigned long long kRepLo = C::REP_LO, kRepHi = C::REP_HI;   // bit r * HW for the ks window rows
 
-        for (int i = 0; i < n_my; ++i) {
+        // What the softmax warps need to know of a tile before its scores arrive: where it lies,
+        // which of its 16-column blocks this warp takes, the validity masks of this thread's query
+        // in both strips, and the query's lse.  It is worked out for tile i + 1 while the dQ MMAs of
+        // tile i run (the warps would only wait there), so that none of it - about 1.8 k cycles of
+        // divisions, 64-bit shifts and a global load - stands between two tiles.
+        struct TileState {
             int bn, r0, c0;
-            decode(i, bn, r0, c0);
-            const uint32_t par = i & 1;
-            const int box_r0 = na2d_ws(g.q_row0 + r0, g.Hg, KS) - g.kv_row0;
-            const int box_c0 = na2d_ws(c0, g.W, KS);
-            const int qr_raw = r0 + (row / TW), qc_raw = c0 + (row % TW);
-            const bool q_valid = qr_raw < g.Hq && qc_raw < g.W;
+            bool q_valid;
+            size_t qi;
+            float lse2;
+            int b_hi, bi_lo;
+            unsigned long long m_lo[2], m_hi[2];
+        };
+        auto prepare = [&](int i) {
+            TileState t;
+            decode(i, t.bn, t.r0, t.c0);
+            const int box_r0 = na2d_ws(g.q_row0 + t.r0, g.Hg, KS) - g.kv_row0;
+            const int box_c0 = na2d_ws(t.c0, g.W, KS);
+            const int qr_raw = t.r0 + (row / TW), qc_raw = t.c0 + (row % TW);
+            t.q_valid = qr_raw < g.Hq && qc_raw < g.W;
             const int qr = min(qr_raw, g.Hq - 1), qc = min(qc_raw, g.W - 1);
-            const size_t qi = (static_cast<size_t>(bn) * g.Hq + qr) * g.W + qc;
+            t.qi = (static_cast<size_t>(t.bn) * g.Hq + qr) * g.W + qc;
             const int wr = na2d_ws(g.q_row0 + qr, g.Hg, KS) - g.kv_row0 - box_r0;   // in [0, TH)
             const int wc = na2d_ws(qc, g.W, KS) - box_c0;                            // in [0, TW)
             const int wr_lo = __shfl_sync(0xffffffffu, wr, 0);
             const int wr_hi = __shfl_sync(0xffffffffu, wr, 31);
-            const float lse2 = lse[qi] * kLog2e;
+            t.lse2 = lse[t.qi] * kLog2e;
             // the warp's queries see strip rows [wr_lo, wr_hi + ks): of the 16-column blocks in that
             // range this warp takes every other one, at most NACT per strip
             const int j_lo = wr_lo * C::HW;
             const int j_hi = min((wr_hi + KS) * C::HW, C::NK);
-            const int b_hi = (j_hi + 15) >> 4;
-            const int bi_lo = ((j_lo >> 4) - half + 1) >> 1;
-
-            uint32_t s[2][NACT][16], dp[2][NACT][16];
-            uint32_t vmask[2][NACT];
-            float d0 = 0.f, d1 = 0.f;
+            t.b_hi = (j_hi + 15) >> 4;
+            t.bi_lo = ((j_lo >> 4) - half + 1) >> 1;
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                const uint32_t t_s = tmem_lane + (x ? C::TMEM_SB : C::TMEM_SA), t_dp = tmem_lane + (x ? C::TMEM_DPB : C::TMEM_DPA);
                 // this query's window columns inside strip x: [cl, chi) of [0, HW); the mask has that
                 // segment in each of its ks window rows
                 const int cl = max(wc - x * C::HW, 0), chi = min(wc + KS - x * C::HW, C::HW);
@@ -307,6 +335,30 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                         shl128(m_lo, m_hi, sh);
                     }
                 }
+                t.m_lo[x] = m_lo;
+                t.m_hi[x] = m_hi;
+            }
+            return t;
+        };
+
+        TileState cur;
+        if (n_my > 0) cur = prepare(0);
+        for (int i = 0; i < n_my; ++i) {
+            const uint32_t par = i & 1;
+            const int bn = cur.bn, r0 = cur.r0, c0 = cur.c0;
+            const bool q_valid = cur.q_valid;
+            const size_t qi = cur.qi;
+            const float lse2 = cur.lse2;
+            const int b_hi = cur.b_hi, bi_lo = cur.bi_lo;
+            if (tid == 0) NA2D_TR(1, 1, i);
+
+            uint32_t s[2][NACT][16], dp[2][NACT][16];
+            uint32_t vmask[2][NACT];
+            float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const uint32_t t_s = tmem_lane + (x ? C::TMEM_SB : C::TMEM_SA), t_dp = tmem_lane + (x ? C::TMEM_DPB : C::TMEM_DPA);
+                const unsigned long long m_lo = cur.m_lo[x], m_hi = cur.m_hi[x];
                 if (tid == 0) NA2D_TR(3, x ? 2 : 0, i);
                 mbar_wait(s_full + x, par, wctx, kErrMmaWait);
                 tc_fence_after();
@@ -394,6 +446,10 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 if (tid == 0) NA2D_TR(3, x ? 6 : 5, i);
             }
 
+            // the next tile's state, under the dQ MMAs
+            TileState nxt = cur;
+            if (i + 1 < n_my) nxt = prepare(i + 1);
+
             // ---- epilogue: this half's columns of the dQ rows of the warp's 32 queries
             mbar_wait(dq_full, par, wctx, kErrMmaWait);
             tc_fence_after();
@@ -411,6 +467,8 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             split_unit(bn, g, hn, hb);
             stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, g.scale, half * DH, c0, r0 + quarter * (32 / TW), hn, hb,
                                     lane);
+            if (tid == 0) NA2D_TR(1, 0, i);
+            cur = nxt;
         }
         if (lane == 0) bulk_wait<0>();          // the staging buffer has been read, the rows written
     }
