@@ -4,6 +4,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <type_traits>
@@ -77,9 +78,12 @@ int check_device(int device) {
 }
 
 // ---- device error word ---------------------------------------------------------------------------
-// One word per device (a file-scope device variable has one instance per device context); bits
-// say which kind of bounded wait gave up.  Kernels get its address as an argument.
-__device__ unsigned int g_error_word = 0;
+// Two words per device (a file-scope device variable has one instance per device context).
+// [0]: bits say which kind of bounded wait gave up; kernels get its address as an argument.
+// [1]: the limit of a bounded wait in microseconds, 0 = the built-in 4 s.  Set once per device from
+// the environment variable NA2D_WAIT_LIMIT_US: a profiler pass that instruments every instruction
+// can stretch a healthy hand-over past the built-in limit (seen under `ncu --set full`).
+__device__ unsigned int g_error_word[2] = {0u, 0u};
 
 // Device address of g_error_word on `device` (which must be current), looked up once per device.
 int error_word_address(int device, unsigned int** out) {
@@ -91,6 +95,14 @@ int error_word_address(int device, unsigned int** out) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_error_word);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_error_word)");
+        if (const char* env = getenv("NA2D_WAIT_LIMIT_US")) {
+            const unsigned long long v = strtoull(env, nullptr, 10);
+            if (v > 0 && v <= 0xffffffffull) {
+                const unsigned int limit = (unsigned int)v;
+                e = cudaMemcpy(static_cast<unsigned int*>(p) + 1, &limit, sizeof(limit), cudaMemcpyHostToDevice);
+                if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(wait limit)");
+            }
+        }
         cache[device] = static_cast<unsigned int*>(p);
     }
     *out = cache[device];
@@ -103,6 +115,7 @@ __global__ void wait_timeout_kernel(unsigned int* err_word, unsigned long long l
     __shared__ na2d_ptx::WaitState state;
     if (threadIdx.x == 0) {
         na2d_ptx::wait_state_init(&state, err_word, limit_ns);
+        state.limit_us = static_cast<uint32_t>(limit_ns / 1000ull);        // the self-test's own limit, whatever is configured
         na2d_ptx::mbar_init(&bar, 1);
         na2d_ptx::mbar_fence_init();
         const na2d_ptx::WaitCtx wctx{&state};
@@ -152,6 +165,12 @@ bool tma_compatible(const Tensor& t) {
     for (long long x : s)
         if (x <= 0 || (x & 7) != 0 || x >= (1ll << 39)) return false;
     return true;
+}
+
+// Pixels per block for the SIMT kernels: 64 (eight per warp, neighbouring windows share L1) unless
+// that gives fewer than two blocks per SM, where one pixel per warp fills the GPU better.
+int simt_patch(long long BN, int H, int W) {
+    return na2d_simt::patch_count(BN, H, W, na2d_simt::kPatch) < 2 * 148 ? na2d_simt::kPatchSmall : na2d_simt::kPatch;
 }
 
 // `key_side`: the call is the key half of the backward, whose key band may be any part of the image
@@ -221,6 +240,7 @@ int make_problem(const na2d_args* a, Problem* out, bool key_side = false) {
         tensor = tc_ok;
     }
     if (!tensor && (C > na2d_simt::kMaxC || ks > na2d_simt::kMaxKs)) return NA2D_ERR_UNSUPPORTED;
+    g.patch = simt_patch(g.BN, g.Hq, W);
     p.g = g; p.B = B; p.dtype = dtype; p.tensor = tensor;
     p.device = a->device; p.st = (cudaStream_t)a->stream;
     p.lse = a->lse; p.delta = a->delta;
@@ -250,8 +270,8 @@ int simt_dispatch(int dtype, int C, F&& f) {
 }
 
 // One block per patch of a (BN, H, W) pixel grid.
-int grid_for(long long BN, int H, int W, unsigned* grid) {
-    const long long nb = na2d_simt::patch_count(BN, H, W);
+int grid_for(long long BN, int H, int W, int patch, unsigned* grid) {
+    const long long nb = na2d_simt::patch_count(BN, H, W, patch);
     if (nb > 0x7fffffffLL) return NA2D_ERR_TOO_LARGE;
     *grid = (unsigned)nb;
     return NA2D_OK;
@@ -290,7 +310,7 @@ int run_forward(const Problem& p) {
         return rc;
     }
     unsigned grid = 0;
-    int rc = grid_for(g.BN, g.Hq, g.W, &grid);
+    int rc = grid_for(g.BN, g.Hq, g.W, g.patch, &grid);
     if (rc != NA2D_OK) return rc;
     return simt_dispatch(p.dtype, g.C, [&](auto tt, auto cpl) -> int {
         using T = typename decltype(tt)::type;
@@ -349,7 +369,7 @@ int run_backward_dq(const Problem& p) {
         return rc;
     }
     unsigned grid = 0;
-    int rc = grid_for(g.BN, g.Hq, g.W, &grid);
+    int rc = grid_for(g.BN, g.Hq, g.W, g.patch, &grid);
     if (rc != NA2D_OK) return rc;
     return simt_dispatch(p.dtype, g.C, [&](auto tt, auto cpl) -> int {
         using T = typename decltype(tt)::type;
@@ -376,7 +396,7 @@ int run_backward_dkdv(const Problem& p) {
         return rc;
     }
     unsigned grid = 0;
-    int rc = grid_for(g.BN, g.Hkv, g.W, &grid);
+    int rc = grid_for(g.BN, g.Hkv, g.W, g.patch, &grid);
     if (rc != NA2D_OK) return rc;
     return simt_dispatch(p.dtype, g.C, [&](auto tt, auto cpl) -> int {
         using T = typename decltype(tt)::type;
@@ -460,6 +480,7 @@ int make_pair_problem(int B, int N, int H, int W, int C, int ks, int dtype, void
     Na2dGeom g;
     g.BN = B * N; g.N = N; g.n_magic = na2d_heads_magic(g.BN, N); g.Hq = H; g.Hkv = H; g.W = W; g.C = C; g.ks = ks; g.kh = ks;
     g.q_row0 = 0; g.kv_row0 = 0; g.Hg = H; g.scale = 1.f; g.sl2 = 1.4426950408889634f;
+    g.patch = simt_patch(g.BN, H, W);
     out->g = g;
     out->dtype = dtype;
     out->st = Na2dStride{(long long)N * H * W * C, (long long)H * W * C, (long long)W * C, C};
@@ -482,7 +503,7 @@ int enter_pair(int B, int N, int H, int W, int C, int ks, int dtype, int device,
 // x . y over the window -> attn
 int pair_dot(const PairProblem& p, const void* x, const void* y, void* attn) {
     unsigned grid = 0;
-    int rc = grid_for(p.g.BN, p.g.Hq, p.g.W, &grid);
+    int rc = grid_for(p.g.BN, p.g.Hq, p.g.W, p.g.patch, &grid);
     if (rc != NA2D_OK) return rc;
     return simt_dispatch(p.dtype, p.g.C, [&](auto tt, auto cpl) -> int {
         using T = typename decltype(tt)::type;
@@ -494,7 +515,7 @@ int pair_dot(const PairProblem& p, const void* x, const void* y, void* attn) {
 // sum_j attn_j y_j -> out
 int pair_apply(const PairProblem& p, const void* attn, const void* y, void* out) {
     unsigned grid = 0;
-    int rc = grid_for(p.g.BN, p.g.Hq, p.g.W, &grid);
+    int rc = grid_for(p.g.BN, p.g.Hq, p.g.W, p.g.patch, &grid);
     if (rc != NA2D_OK) return rc;
     return simt_dispatch(p.dtype, p.g.C, [&](auto tt, auto cpl) -> int {
         using T = typename decltype(tt)::type;
@@ -507,7 +528,7 @@ int pair_apply(const PairProblem& p, const void* attn, const void* y, void* out)
 // key-side sum over the inverse neighbourhood of attn x -> out
 int pair_inverse(const PairProblem& p, const void* attn, const void* x, void* out) {
     unsigned grid = 0;
-    int rc = grid_for(p.g.BN, p.g.Hkv, p.g.W, &grid);
+    int rc = grid_for(p.g.BN, p.g.Hkv, p.g.W, p.g.patch, &grid);
     if (rc != NA2D_OK) return rc;
     return simt_dispatch(p.dtype, p.g.C, [&](auto tt, auto cpl) -> int {
         using T = typename decltype(tt)::type;
@@ -723,6 +744,8 @@ int na2d_check(int device, void* stream) {
     if (word != 0) {
         NA2D_CUDA(cudaMemsetAsync(addr, 0, sizeof(word), st));
         NA2D_CUDA(cudaStreamSynchronize(st));
+        snprintf(t_cuda_err, sizeof(t_cuda_err),
+                 "device error word 0x%x (1: load wait, 2: MMA wait, 4: other wait, 8: shared memory base not 1024-byte aligned)", word);
         return NA2D_ERR_KERNEL_WAIT;
     }
     return NA2D_OK;

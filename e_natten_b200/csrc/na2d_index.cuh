@@ -46,6 +46,7 @@ struct Na2dGeom {
     int q_row0;    // global row of query-side row 0
     int kv_row0;   // global row of key-side row 0
     int Hg;        // rows of the whole image
+    int patch;     // SIMT kernels: pixels per block, 64 (8 per warp) or 8 (1 per warp, small grids)
     float scale;   // softmax scale: the logits are scale * (q . k)
     float sl2;     // scale * log2(e)
 };

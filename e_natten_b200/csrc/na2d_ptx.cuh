@@ -14,7 +14,8 @@ namespace na2d_ptx {
 enum : unsigned int {
     kErrLoadWait = 1u,      // a TMA load barrier did not complete
     kErrMmaWait = 2u,       // an MMA commit barrier did not complete
-    kErrOther = 4u
+    kErrOther = 4u,
+    kErrSmemBase = 8u       // the dynamic shared memory did not start on a 1024-byte boundary
 };
 
 // A waiting thread is suspended by the hardware inside mbarrier.try_wait for up to kWaitHintNs
@@ -55,7 +56,9 @@ __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
 }
 __device__ __forceinline__ void wait_state_init(WaitState* st, unsigned int* err_word, unsigned long long limit_ns) {
     st->abort = 0;
-    st->limit_us = static_cast<uint32_t>(limit_ns / 1000ull);
+    // err_word[1], when set, overrides the limit (microseconds)
+    const uint32_t configured = err_word[1];
+    st->limit_us = configured != 0u ? configured : static_cast<uint32_t>(limit_ns / 1000ull);
     st->err_word = err_word;
 }
 

@@ -35,7 +35,8 @@
 namespace na2d_simt {
 
 constexpr int kWarps = 8;          // warps per block
-constexpr int kPatch = 64;         // pixels per block
+constexpr int kPatch = 64;         // pixels per block (8 per warp); kPatchSmall where that leaves most SMs empty
+constexpr int kPatchSmall = 8;     // one pixel per warp
 constexpr int kMaxC = 256;         // head dim limit of the SIMT path
 constexpr int kMaxKs = 31;         // kernel size limit of the SIMT path
 
@@ -77,11 +78,13 @@ __device__ __forceinline__ float transpose_sum32(float (&v)[32], int lane) {
     return v[0];
 }
 
-// Patches of a (BN, H, W) pixel grid: 8 x 8 pixels, or 1 x 64 for a one-row image.
-__host__ __device__ __forceinline__ int patch_h(int H) { return H == 1 ? 1 : 8; }
-__host__ __device__ __forceinline__ int patch_w(int H) { return kPatch / patch_h(H); }
-inline long long patch_count(long long BN, int H, int W) {
-    return BN * ((H + patch_h(H) - 1) / patch_h(H)) * ((W + patch_w(H) - 1) / patch_w(H));
+// Patches of a (BN, H, W) pixel grid: 8 x 8 pixels (2 x 4 for the small patch), or one row of
+// `patch` pixels for a one-row image.
+__host__ __device__ __forceinline__ int patch_h(int H, int patch) { return H == 1 ? 1 : (patch == kPatch ? 8 : 2); }
+__host__ __device__ __forceinline__ int patch_w(int H, int patch) { return patch / patch_h(H, patch); }
+inline long long patch_count(long long BN, int H, int W, int patch) {
+    const int ph = patch_h(H, patch), pw = patch_w(H, patch);
+    return BN * ((H + ph - 1) / ph) * ((W + pw - 1) / pw);
 }
 
 // A pixel's coordinates and its index in the dense (BN, H, W) arrays (lse, delta, attn).
@@ -90,8 +93,8 @@ struct Pixel {
     int b, n, h, w;
 };
 // Pixel t of the block's patch; false if it lies outside the grid.
-__device__ __forceinline__ bool patch_pixel(Pixel& p, int t, int H, int W, int N) {
-    const int ph = patch_h(H), pw = patch_w(H);
+__device__ __forceinline__ bool patch_pixel(Pixel& p, int t, int H, int W, int N, int patch) {
+    const int ph = patch_h(H, patch), pw = patch_w(H, patch);
     const int tiles_w = (W + pw - 1) / pw, tiles_h = (H + ph - 1) / ph;
     long long blk = blockIdx.x;
     const int tw = (int)(blk % tiles_w);
@@ -186,9 +189,9 @@ fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kh = g.kh, kw = g.ks, nk = kh * kw;
     float* ss = smem + warp * nk;
-    for (int t = warp; t < kPatch; t += kWarps) {
+    for (int t = warp; t < g.patch; t += kWarps) {
     Pixel px;
-    if (!patch_pixel(px, t, g.Hq, g.W, g.N)) continue;          // warp-uniform; no block barrier anywhere
+    if (!patch_pixel(px, t, g.Hq, g.W, g.N, g.patch)) continue;          // warp-uniform; no block barrier anywhere
     const long long qi = px.idx;
     const int oh = na2d_ws(g.q_row0 + px.h, g.Hg, kh) - g.kv_row0;
     const int ow = na2d_ws(px.w, g.W, kw);
@@ -237,9 +240,9 @@ dq_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict_
     const int kh = g.kh, kw = g.ks, nk = kh * kw;
     float* ps = smem + warp * 2 * nk;          // p per window member, then dS
     float* dps = ps + nk;                      // dP per window member
-    for (int t = warp; t < kPatch; t += kWarps) {
+    for (int t = warp; t < g.patch; t += kWarps) {
     Pixel px;
-    if (!patch_pixel(px, t, g.Hq, g.W, g.N)) continue;
+    if (!patch_pixel(px, t, g.Hq, g.W, g.N, g.patch)) continue;
     const long long qi = px.idx;
     const int oh = na2d_ws(g.q_row0 + px.h, g.Hg, kh) - g.kv_row0;
     const int ow = na2d_ws(px.w, g.W, kw);
@@ -304,9 +307,9 @@ dkdv_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restric
             const Na2dStride sdk, const Na2dStride sdv, const Na2dGeom g) {
     __shared__ float s_p[kWarps][32], s_ds[kWarps][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int t = warp; t < kPatch; t += kWarps) {
+    for (int t = warp; t < g.patch; t += kWarps) {
     Pixel px;
-    if (!patch_pixel(px, t, g.Hkv, g.W, g.N)) continue;
+    if (!patch_pixel(px, t, g.Hkv, g.W, g.N, g.patch)) continue;
     const Inverse iv = inverse_neighbourhood(g.kv_row0 + px.h, px.w, g);
     const int n_in = iv.nr * iv.nc;
 
@@ -376,9 +379,9 @@ window_dot_kernel(const T* __restrict__ x, const T* __restrict__ y, T* __restric
                   const Na2dStride sy, const Na2dGeom g) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kh = g.kh, kw = g.ks, nk = kh * kw;
-    for (int t = warp; t < kPatch; t += kWarps) {
+    for (int t = warp; t < g.patch; t += kWarps) {
     Pixel px;
-    if (!patch_pixel(px, t, g.Hq, g.W, g.N)) continue;
+    if (!patch_pixel(px, t, g.Hq, g.W, g.N, g.patch)) continue;
     const long long qi = px.idx;
     const int oh = na2d_ws(g.q_row0 + px.h, g.Hg, kh) - g.kv_row0;
     const int ow = na2d_ws(px.w, g.W, kw);
@@ -402,9 +405,9 @@ window_apply_kernel(const T* __restrict__ attn, const T* __restrict__ y, T* __re
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kh = g.kh, kw = g.ks, nk = kh * kw;
     float* ws = smem + warp * nk;
-    for (int t = warp; t < kPatch; t += kWarps) {
+    for (int t = warp; t < g.patch; t += kWarps) {
     Pixel px;
-    if (!patch_pixel(px, t, g.Hq, g.W, g.N)) continue;
+    if (!patch_pixel(px, t, g.Hq, g.W, g.N, g.patch)) continue;
     const long long qi = px.idx;
     const int oh = na2d_ws(g.q_row0 + px.h, g.Hg, kh) - g.kv_row0;
     const int ow = na2d_ws(px.w, g.W, kw);
@@ -428,9 +431,9 @@ window_inverse_kernel(const T* __restrict__ attn, const T* __restrict__ x, T* __
                       const Na2dStride so, const Na2dGeom g) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kh = g.kh, kw = g.ks, nk = kh * kw;
-    for (int t = warp; t < kPatch; t += kWarps) {
+    for (int t = warp; t < g.patch; t += kWarps) {
     Pixel px;
-    if (!patch_pixel(px, t, g.Hkv, g.W, g.N)) continue;
+    if (!patch_pixel(px, t, g.Hkv, g.W, g.N, g.patch)) continue;
     const int key_row = g.kv_row0 + px.h;
     const Inverse iv = inverse_neighbourhood(key_row, px.w, g);
     float acc[CPL];

@@ -177,19 +177,29 @@ template <int DH> struct OutStage {
 // Stores columns [0, DH) held as fp32 bit patterns in `v` (scaled by `scale`) as 16-bit channels
 // [ch0, ch0 + DH) of the warp's 32 pixels, whose first tile row is image row h0 and first column w0,
 // of head n of batch b.
-template <typename DT, int DH>
+// NBUF staging buffers of OutStage<DH>::BYTES lie one after another at `stage`; `seq` counts the
+// warp's rounds and picks the buffer.  With one buffer a round waits until the previous round's
+// store has read it (several hundred cycles per round); with two it only waits for the round
+// before that.
+// SCALED = false stores the values as they are (`scale` is ignored).
+template <typename DT, int DH, int NBUF = 1, bool SCALED = true>
 __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint8_t* stage, const uint32_t (&v)[DH],
-                                                float scale, int ch0, int w0, int h0, int n, int b, int lane) {
+                                                float scale, int ch0, int w0, int h0, int n, int b, int lane,
+                                                uint32_t* seq = nullptr) {
     using S = OutStage<DH>;
-    const uint32_t row = smem_u32(stage) + lane * S::ROWB;
+    static_assert(NBUF == 1 || NBUF == 2, "one or two staging buffers");
     const int sw = S::ROWB == 64 ? ((lane >> 1) & 3) : ((lane >> 2) & 1);
 #pragma unroll
     for (int r = 0; r < S::ROUNDS; ++r) {
         uint32_t w[S::RW / 2];
 #pragma unroll
         for (int e = 0; e < S::RW / 2; ++e)
-            w[e] = pack2<DT>(__uint_as_float(v[r * S::RW + 2 * e]) * scale, __uint_as_float(v[r * S::RW + 2 * e + 1]) * scale);
-        if (lane == 0) bulk_wait_read<0>();             // the previous store has read the buffer
+            w[e] = SCALED ? pack2<DT>(__uint_as_float(v[r * S::RW + 2 * e]) * scale, __uint_as_float(v[r * S::RW + 2 * e + 1]) * scale)
+                          : pack2<DT>(__uint_as_float(v[r * S::RW + 2 * e]), __uint_as_float(v[r * S::RW + 2 * e + 1]));
+        const uint32_t buf = NBUF == 1 ? 0u : ((*seq)++ & 1u);
+        const uint32_t base = smem_u32(stage) + buf * S::BYTES;
+        const uint32_t row = base + lane * S::ROWB;
+        if (lane == 0) bulk_wait_read<NBUF - 1>();      // the store that last used this buffer has read it
         __syncwarp();
 #pragma unroll
         for (int c = 0; c < S::ROWB / 16; ++c)
@@ -197,7 +207,7 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint8_t*
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-            tma_store_5d(map, smem_u32(stage), ch0 + r * S::RW, w0, h0, n, b);
+            tma_store_5d(map, base, ch0 + r * S::RW, w0, h0, n, b);
             bulk_commit();
         }
     }
@@ -205,27 +215,36 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, uint8_t*
 
 // The same with fp32 output (the partial dK / dV of a row band, which its owner adds to its own):
 // rounds of 16 channels, again 64-byte rows in the 64-byte swizzle of an fp32 tensor map whose box
-// is 16 channels wide.
-template <int NCOL>
+// is 16 channels wide.  Buffers of 2 KB each.
+template <int NCOL, int NBUF = 1, bool SCALED = true>
 __device__ __forceinline__ void stage_and_store_f32(const CUtensorMap* map, uint8_t* stage, const uint32_t (&v)[NCOL],
-                                                    float scale, int ch0, int w0, int h0, int n, int b, int lane) {
+                                                    float scale, int ch0, int w0, int h0, int n, int b, int lane,
+                                                    uint32_t* seq = nullptr) {
     static_assert(NCOL % 16 == 0, "rounds of 16 channels");
-    const uint32_t row = smem_u32(stage) + lane * 64;
+    static_assert(NBUF == 1 || NBUF == 2, "one or two staging buffers");
     const int sw = (lane >> 1) & 3;
 #pragma unroll
     for (int r = 0; r < NCOL / 16; ++r) {
-        if (lane == 0) bulk_wait_read<0>();             // the previous store has read the buffer
+        const uint32_t buf = NBUF == 1 ? 0u : ((*seq)++ & 1u);
+        const uint32_t base = smem_u32(stage) + buf * 2048u;
+        const uint32_t row = base + lane * 64;
+        if (lane == 0) bulk_wait_read<NBUF - 1>();      // the store that last used this buffer has read it
         __syncwarp();
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-            st_shared_v4(row + ((c ^ sw) << 4), __float_as_uint(__uint_as_float(v[16 * r + 4 * c]) * scale),
-                         __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 1]) * scale),
-                         __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 2]) * scale),
-                         __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 3]) * scale));
+        for (int c = 0; c < 4; ++c) {
+            if (SCALED)
+                st_shared_v4(row + ((c ^ sw) << 4), __float_as_uint(__uint_as_float(v[16 * r + 4 * c]) * scale),
+                             __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 1]) * scale),
+                             __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 2]) * scale),
+                             __float_as_uint(__uint_as_float(v[16 * r + 4 * c + 3]) * scale));
+            else
+                st_shared_v4(row + ((c ^ sw) << 4), v[16 * r + 4 * c], v[16 * r + 4 * c + 1], v[16 * r + 4 * c + 2],
+                             v[16 * r + 4 * c + 3]);
+        }
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-            tma_store_5d(map, smem_u32(stage), ch0 + 16 * r, w0, h0, n, b);
+            tma_store_5d(map, base, ch0 + 16 * r, w0, h0, n, b);
             bulk_commit();
         }
     }

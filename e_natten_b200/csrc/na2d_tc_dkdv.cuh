@@ -5,7 +5,7 @@
 // neighbourhoods, clipped to the local query band), walked in chunks of RC rows x HW columns
 // (at most 64 queries):
 //     S^T = K Q_c^T,  dP^T = V dO_c^T                      (tensor memory, fp32)
-//     P^T = exp(S^T - lse),  dS^T = P^T (dP^T - delta)     (softmax warps, registers)
+//     P^T = exp(S^T - lse),  dS^T = scale P^T (dP^T - delta)   (softmax warps, registers; the scale is dK's)
 //     dV += P^T dO_c,  dK += dS^T Q_c                      (P^T, dS^T read from tensor memory)
 // P^T and dS^T are written back over S^T / dP^T as packed 16-bit pairs; on the bf16 path dS^T
 // is written as head + residual (two MMAs), because one bf16 keeps too few bits for dK.
@@ -50,7 +50,7 @@ struct DkvCfg : Cfg<D, KS, 64, 0, dkv_w_split(KS)> {
     static constexpr int TMEM_ST = 0, TMEM_DPT = 64, TMEM_DV = 256, TMEM_DK = 384;
     static constexpr int TMEM_PT = 0, TMEM_DST = 32, TMEM_RES = 64;       // 16-bit operands over S^T / dP^T
     static constexpr int STAGE = 2 * B::KV_BYTES;                          // Q chunk then dO chunk
-    static constexpr int OUT_BYTES = 4 * OutStage<32>::BYTES;              // staging of the 4 epilogue warps
+    static constexpr int OUT_BYTES = 4 * 2 * OutStage<32>::BYTES;          // two staging buffers for each of the 4 epilogue warps
     static constexpr int XCHG_BYTES = 2 * 2 * 2 * 64 * 4;                  // [group][parity]{lse, delta}[64]
     static constexpr int FIXED = 2 * B::Q_BYTES /*K, V tile*/ + OUT_BYTES + XCHG_BYTES + 256 + 1024;
     static constexpr int NSTQ = (FIXED + 4 * STAGE <= kSmemLimit) ? 4 : 3;
@@ -83,14 +83,15 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
     uint64_t* kv_full = bars + 0;            //       TMA -> MMA
     uint64_t* kv_empty = bars + 1;           //       MMA (commit) -> TMA
     uint64_t* acc_full = bars + 2;           //       MMA (commit) -> epilogue
-    uint64_t* acc_free = bars + 3;           //       epilogue -> MMA
+    uint64_t* acc_free = bars + 3;           //       epilogue -> MMA: dV and dK have been read
     uint64_t* s_full = bars + 4;             // [2]   MMA (commit) -> softmax group
     uint64_t* p_full = bars + 6;             // [2]   softmax group -> MMA
     uint64_t* qd_full = bars + 8;            // [4]   TMA -> MMA
     uint64_t* qd_empty = bars + 12;          // [4]   MMA (commit) -> TMA
     uint64_t* st_free = bars + 16;           // [2]   output MMAs (commit) -> score MMAs: the stage is free
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
-    const WaitCtx wctx{reinterpret_cast<WaitState*>(bars + 19)};
+    uint64_t* accv_free = bars + 18;         //       epilogue -> MMA: dV has been read (dK follows)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+    const WaitCtx wctx{reinterpret_cast<WaitState*>(bars + 20)};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_my = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -101,6 +102,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         mbar_init(kv_empty, 1);
         mbar_init(acc_full, 1);
         mbar_init(acc_free, 4);
+        mbar_init(accv_free, 4);
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full + i, 1);
             mbar_init(p_full + i, 8);
@@ -257,15 +259,30 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 const uint32_t tm = tmem_base + (n & 1) * C::TMEM_STAGE;
                 const uint32_t acc = ch == 0 ? 0u : 1u;
                 mbar_wait(p_full + (n & 1), (n >> 1) & 1, wctx, kErrMmaWait);
-                if (ch == 0) mbar_wait(acc_free, (it & 1) ^ 1, wctx, kErrMmaWait);
+                if (ch == 0) {
+                    // A tile's first chunk overwrites the accumulators the epilogue warps are still
+                    // reading out for the previous tile.  They read dV first and say so, so its dV
+                    // MMAs go ahead of its dK MMAs and only the latter wait for the whole read-out.
+                    mbar_wait(accv_free, (it & 1) ^ 1, wctx, kErrMmaWait);
+                    tc_fence_after();
+                    if (elect_one()) {
+#pragma unroll
+                        for (int kk = 0; kk < C::NKP / 16; ++kk)
+                            umma_ts(tmem_base + C::TMEM_DV, tm + C::TMEM_PT + 8 * kk,
+                                    desc64(hi, gm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, kk > 0);
+                    }
+                    __syncwarp();
+                    mbar_wait(acc_free, (it & 1) ^ 1, wctx, kErrMmaWait);
+                }
                 tc_fence_after();
                 if (elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < C::NKP / 16; ++kk) {               // dK and dV chains alternate
                         umma_ts(tmem_base + C::TMEM_DK, tm + C::TMEM_DST + 8 * kk,
                                 desc64(hi, qm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
-                        umma_ts(tmem_base + C::TMEM_DV, tm + C::TMEM_PT + 8 * kk,
-                                desc64(hi, gm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, acc | (kk > 0));
+                        if (ch != 0)
+                            umma_ts(tmem_base + C::TMEM_DV, tm + C::TMEM_PT + 8 * kk,
+                                    desc64(hi, gm_lo + ((kk * 16 * C::ROWB) >> 4)), idesc_o, 1u);
                     }
                     if (SPLIT) {
 #pragma unroll
@@ -318,9 +335,9 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
         reg_dec<kDkvRegsEpi>();
         const int quarter = warp & 3;
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        uint8_t* stage = sOut + quarter * OutStage<32>::BYTES;
+        uint8_t* stage = sOut + quarter * 2 * OutStage<32>::BYTES;
         constexpr int RPO = D / 32;                          // 32-channel rounds per output
-        uint32_t it = 0;
+        uint32_t it = 0, seq = 0;
         for (int i = 0; i < n_my; ++i) {
             const TileGeo t = tile_geo(i);
             if (t.n_ch == 0) {                               // no local query sees this tile: zeros
@@ -330,11 +347,11 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
 #pragma unroll
                 for (int j = 0; j < 2 * RPO; ++j) {
                     if (f32_out)
-                        stage_and_store_f32<32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
-                                                t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane);
+                        stage_and_store_f32<32, 2>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
+                                                   t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane, &seq);
                     else
-                        stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
-                                                t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane);
+                        stage_and_store<DT, 32, 2>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, z, 1.f, 32 * (j % RPO), t.kc0,
+                                                   t.kr0 + quarter * (32 / TW), t.hn, t.hb, lane, &seq);
                 }
                 continue;
             }
@@ -349,6 +366,11 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 2 * RPO; ++j) {
                 tmem_ld_wait();
+                if (j == RPO - 1) {                          // dV is in registers (or stored)
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(accv_free);
+                }
                 if (j + 1 < 2 * RPO) {
                     const int which = (j + 1) / RPO, r = (j + 1) % RPO;
                     tmem_ld_32x32(tmem_lane + (which == 0 ? C::TMEM_DV : C::TMEM_DK) + 32 * r, v[(j + 1) & 1]);
@@ -358,14 +380,13 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                     if (lane == 0) mbar_arrive(acc_free);
                     if (warp == 12 && lane == 0) NA2D_TR(0, 2, it);
                 }
-                // dK = scale * sum_i p (dP - delta) q: the softmax scale goes in here, once per output
-                const float out_scale = j / RPO == 0 ? 1.f : g.scale;
+                // (the softmax scale of dK is already in dS^T: the epilogue only converts)
                 if (f32_out)
-                    stage_and_store_f32<32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], out_scale, 32 * (j % RPO), t.kc0,
-                                            h0, t.hn, t.hb, lane);
+                    stage_and_store_f32<32, 2, false>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 1.f, 32 * (j % RPO),
+                                                      t.kc0, h0, t.hn, t.hb, lane, &seq);
                 else
-                    stage_and_store<DT, 32>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], out_scale, 32 * (j % RPO), t.kc0,
-                                            h0, t.hn, t.hb, lane);
+                    stage_and_store<DT, 32, 2, false>(j / RPO == 0 ? &tm_dv : &tm_dk, stage, v[j & 1], 1.f, 32 * (j % RPO),
+                                                      t.kc0, h0, t.hn, t.hb, lane, &seq);
             }
             if (warp == 12 && lane == 0) NA2D_TR(0, 3, it);
             ++it;
@@ -443,7 +464,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                 float* x_delta = x_lse + 64;
                 if (gtid < C::NK) {
                     x_lse[gtid] = pre_l2 * kLog2e;
-                    x_delta[gtid] = pre_dl;
+                    x_delta[gtid] = pre_dl * g.scale;       // dS^T carries the softmax scale of dK: scale p (dP - delta)
                 }
                 // the warp's keys are seen from chunk rows [ra, rb): its active column range
                 const int ra = max(wrow_lo - r_off, 0), rb = min(wrow_hi - r_off, C::RC);
@@ -530,7 +551,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CU
                                 const float pe = fast_exp2(fmaf(__uint_as_float(s[a][e]), g.sl2, -l2[e]));
                                 const bool ok = (vmask >> e) & 1u;         // select, never multiply by zero
                                 p[h] = ok ? pe : 0.f;
-                                ds[h] = ok ? pe * (__uint_as_float(dp[a][e]) - dl[e]) : 0.f;
+                                ds[h] = ok ? pe * fmaf(__uint_as_float(dp[a][e]), g.scale, -dl[e]) : 0.f;
                             }
                             wp[e2] = pack2<DT>(p[0], p[1]);
                             wd[e2] = pack2<DT>(ds[0], ds[1]);

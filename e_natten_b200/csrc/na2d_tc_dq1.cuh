@@ -5,7 +5,7 @@
 // is cut into a left strip A and a right strip B (box rows x half the box columns each):
 //     S_x = Q K_x^T,  dP_x = dO V_x^T          (x = A, B; four accumulators fill tensor memory)
 //     p = exp(S - lse),  delta = sum_j p_j dP_j over both strips     (softmax warps, registers)
-//     dS_x = p_x (dP_x - delta)  ->  tensor memory, over dP_x         (head + residual on bf16)
+//     dS_x = scale p_x (dP_x - delta)  ->  tensor memory, over dP_x   (head + residual on bf16)
 //     dQ = dS_A K_A + dS_B K_B                  (accumulated over S_B, which is in registers by then)
 // Splitting the box lets the tensor pipe work under the softmax warps: the score MMAs of strip B
 // run while strip A is read, dS_A K_A runs while dS_B is formed, and the score MMAs of the next
@@ -24,8 +24,12 @@ struct Dq1Cfg : Cfg<D, KS, 128, 0, 2> {
     static_assert(B::NCH == 1, "a strip must hold all box rows");
     static constexpr int TMEM_SA = 0, TMEM_DPA = 128, TMEM_SB = 256, TMEM_DPB = 384;
     static constexpr int TMEM_DQ = TMEM_SB;                               // dQ accumulates over S_B
-    static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;          // output staging of the 8 softmax warps
-    static constexpr int SMEM = 2 * B::Q_BYTES + 4 * B::KV_BYTES + OUT_BYTES + 2 * 2 * 128 * 4 + 256 + 1024;
+    // Two output staging buffers for each of the 8 softmax warps where they fit.  They only fit
+    // (head dim 128) because the kernel asks for its dynamic shared memory on a 1024-byte boundary
+    // instead of keeping 1024 bytes of slack to round the base up itself.
+    static constexpr int NOUT = (2 * B::Q_BYTES + 4 * B::KV_BYTES + 16 * OutStage<D / 2>::BYTES + 2 * 2 * 128 * 4 + 256 <= kSmemLimit) ? 2 : 1;
+    static constexpr int OUT_BYTES = 8 * NOUT * OutStage<D / 2>::BYTES;
+    static constexpr int SMEM = 2 * B::Q_BYTES + 4 * B::KV_BYTES + OUT_BYTES + 2 * 2 * 128 * 4 + 256;
     static constexpr int NB16 = B::NKP / 16;
     static constexpr unsigned long long REP_LO = row_repeat_lo(B::HW, KS), REP_HI = row_repeat_hi(B::HW, KS);
     static_assert(SMEM <= kSmemLimit, "dQ strip kernel shared memory");
@@ -41,8 +45,12 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
            const int total_tiles) {
     constexpr bool SPLIT = IsBf16<DT>::value;
     using C = Dq1Cfg<D, KS, SPLIT>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    if (smem_u32(smem_raw) & 1023u) {                 // the swizzled operand layouts need it; never seen
+        if (threadIdx.x == 0) atomicOr(err_word, kErrSmemBase);
+        return;
+    }
     uint8_t* sQ = smem;
     uint8_t* sDO = sQ + C::Q_BYTES;
     uint8_t* sStrip = sDO + C::Q_BYTES;               // 4 strip buffers [NKP x D]
@@ -159,21 +167,6 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     for (int sl = 0; sl < C::NS; ++sl) {
                         if (j & 1) tma_load_5d(dst + sl * C::KV_SLAB, &tm_v, st_full + slot[j], sl * 64, box_c0 + (j >> 1) * C::HW, box_r0, hn, hb);
                         else tma_load_5d(dst + sl * C::KV_SLAB, &tm_k, st_full + slot[j], sl * 64, box_c0 + (j >> 1) * C::HW, box_r0, hn, hb);
-                    }
-                }
-                // The buffers of the next tile's K_B and V_B are only free after this tile's dQ MMAs,
-                // and a load from HBM issued then is what the next tile's strip B would wait for:
-                // bring those two strips into L2 now.
-                if (i + 1 < n_my && lt.ok) {
-                    int bn2, r2, c2, hn2, hb2;
-                    decode(i + 1, bn2, r2, c2);
-                    split_unit(bn2, g, hn2, hb2);
-                    const int nr0 = na2d_ws(g.q_row0 + r2, g.Hg, KS) - g.kv_row0;
-                    const int nc0 = na2d_ws(c2, g.W, KS) + C::HW;
-#pragma unroll
-                    for (int sl = 0; sl < C::NS; ++sl) {
-                        tma_prefetch_5d(&tm_k, sl * 64, nc0, nr0, hn2, hb2);
-                        tma_prefetch_5d(&tm_v, sl * 64, nc0, nr0, hn2, hb2);
                     }
                 }
             }
@@ -342,6 +335,7 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         };
 
         TileState cur;
+        uint32_t out_seq = 0;
         if (n_my > 0) cur = prepare(0);
         for (int i = 0; i < n_my; ++i) {
             const uint32_t par = i & 1;
@@ -407,7 +401,9 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             const float dl = (d0 + d1) + x_sum[(par * 2 + (half ^ 1)) * 128 + row];
             if (q_valid && half == 0) delta[qi] = dl;
 
-            // dS = p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path)
+            // dS = scale p (dP - delta) as packed 16-bit pairs (head, and residual on the bf16 path); the
+            // softmax scale of dQ goes in here, inside a multiply-add that replaces the subtraction
+            const float dls = dl * g.scale;
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
                 const uint32_t t_ds = tmem_lane + (x ? C::TMEM_DPB : C::TMEM_DPA);
@@ -419,8 +415,8 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                         for (int e2 = 0; e2 < 8; ++e2) {
                             // p and dP of masked columns are exact zeros here
-                            const float ds0 = __uint_as_float(s[x][a][2 * e2]) * (__uint_as_float(dp[x][a][2 * e2]) - dl);
-                            const float ds1 = __uint_as_float(s[x][a][2 * e2 + 1]) * (__uint_as_float(dp[x][a][2 * e2 + 1]) - dl);
+                            const float ds0 = __uint_as_float(s[x][a][2 * e2]) * fmaf(__uint_as_float(dp[x][a][2 * e2]), g.scale, -dls);
+                            const float ds1 = __uint_as_float(s[x][a][2 * e2 + 1]) * fmaf(__uint_as_float(dp[x][a][2 * e2 + 1]), g.scale, -dls);
                             wd[e2] = pack2<DT>(ds0, ds1);
                             wr2[e2] = SPLIT ? pack2_residual_bf16(ds0, ds1, wd[e2]) : 0u;
                         }
@@ -462,11 +458,10 @@ dq1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) mbar_arrive(dq_free);
             if (tid == 0) NA2D_TR(3, 7, i);
-            // dQ = scale * sum_j p (dP - delta) k: the softmax scale goes in here, once per output
             int hn, hb;
             split_unit(bn, g, hn, hb);
-            stage_and_store<DT, DH>(&tm_dq, sOut + warp * OutStage<DH>::BYTES, acc, g.scale, half * DH, c0, r0 + quarter * (32 / TW), hn, hb,
-                                    lane);
+            stage_and_store<DT, DH, C::NOUT, false>(&tm_dq, sOut + warp * C::NOUT * OutStage<DH>::BYTES, acc, 1.f, half * DH, c0,
+                                                    r0 + quarter * (32 / TW), hn, hb, lane, &out_seq);
             if (tid == 0) NA2D_TR(1, 0, i);
             cur = nxt;
         }

@@ -43,7 +43,7 @@ struct FwdCfg : Cfg<D, KS, 192> {
     static constexpr int K_BYTES = B::NS * K_SLAB;
     static constexpr int V_BYTES = B::KV_BYTES;
     static constexpr int XCHG_BYTES = 4 * 2 * 128 * 4;                  // row max [2][2][128], row sum [2][2][128]
-    static constexpr int OUT_BYTES = 8 * OutStage<D / 2>::BYTES;         // output staging of the 8 softmax warps
+    static constexpr int OUT_BYTES = 8 * 2 * OutStage<D / 2>::BYTES;     // two output staging buffers for each of the 8 softmax warps
     static constexpr int FIXED = XCHG_BYTES + OUT_BYTES + 256 /*barriers*/ + 1024 /*alignment*/;
     // Ring depths, given out in the order that pays most: a second V slot first (a V slot is only
     // free after the chunk's last MMA, so its refill is what the next tile would wait for), then a
@@ -269,7 +269,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         constexpr int DH = D / 2;                // output columns of this half
         // epilogue of the previous tile, deferred until the next tile's first chunk is under way
         bool pend = false, pend_valid = false;
-        uint32_t pend_tile = 0;
+        uint32_t pend_tile = 0, out_seq = 0;
         float pend_max = 0.f, pend_sum = 1.f;
         size_t pend_qi = 0;
         int pend_bn = 0, pend_r0 = 0, pend_c0 = 0;
@@ -292,8 +292,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             if (lane == 0) mbar_arrive(o_free + ob);                         // O is in registers
             int hn, hb;
             split_unit(pend_bn, g, hn, hb);
-            stage_and_store<DT, DH>(&tm_o, sOut + warp * OutStage<DH>::BYTES, acc, inv, half * DH, pend_c0,
-                                    pend_r0 + quarter * (32 / TW), hn, hb, lane);
+            stage_and_store<DT, DH, 2>(&tm_o, sOut + warp * 2 * OutStage<DH>::BYTES, acc, inv, half * DH, pend_c0,
+                                       pend_r0 + quarter * (32 / TW), hn, hb, lane, &out_seq);
             if (pend_valid && half == 0) lse[pend_qi] = (pend_max + log2f(total)) * kLn2;
             pend = false;
         };
