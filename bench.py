@@ -152,6 +152,10 @@ class ClockSampler:
         # the headline's timed region is a few tens of milliseconds; the other timed regions of the
         # same run (end to end, sweep) give the record under load that a sample count needs
         out["all_timed_regions"] = self._summary(every)
+        if out["samples"] == 0 and every:
+            # an NVML query takes milliseconds: a headline region of a few steps can end between two
+            out.update({k: out["all_timed_regions"][k] for k in ("sm_mhz", "reasons")})
+            out["window"] = "no sample fell inside the headline region; figures of all timed regions of this run"
         return out
 
 
