@@ -44,6 +44,11 @@ class Args(C.Structure):
 
 OP_2D, OP_1D = 0, 1
 FLAG_DKDV_F32 = 1
+
+
+def flag_sm_margin(n: int) -> int:
+    """NA2D_FLAG_SM_MARGIN(n): the persistent kernels leave ``n`` SMs to a kernel running beside them."""
+    return (int(n) & 0xFF) << 8
 _DENSE = [C.c_int] * 7 + [C.POINTER(Rows), C.c_int, C.c_int, C.c_void_p]      # B..dtype, rows, path, device, stream
 _PAIR = [C.c_int] * 7 + [C.c_int, C.c_void_p]                                  # B..dtype, device, stream
 

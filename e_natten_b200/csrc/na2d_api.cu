@@ -135,6 +135,7 @@ struct Problem {
     int dtype = 0;
     bool tensor = false;      // run the tcgen05 kernels
     bool dkdv_f32 = false;    // dK / dV are fp32 tensors
+    int sm_margin = 0;        // SMs the persistent kernels leave free
     int device = 0;
     cudaStream_t st = nullptr;
     Tensor q, k, v, o, d_o, d_q, d_k, d_v;
@@ -245,7 +246,8 @@ int make_problem(const na2d_args* a, Problem* out, bool key_side = false) {
     p.device = a->device; p.st = (cudaStream_t)a->stream;
     p.lse = a->lse; p.delta = a->delta;
     p.dkdv_f32 = (a->flags & NA2D_FLAG_DKDV_F32) != 0 && dtype != NA2D_F32;
-    if (a->flags & ~NA2D_FLAG_DKDV_F32) return NA2D_ERR_BAD_ARG;
+    p.sm_margin = (a->flags >> 8) & 0xff;
+    if (a->flags & ~(NA2D_FLAG_DKDV_F32 | NA2D_FLAG_SM_MARGIN(0xff))) return NA2D_ERR_BAD_ARG;
     return NA2D_OK;
 }
 
@@ -291,7 +293,7 @@ int launch_ctx(const Problem& p, int* launched, na2d_tc::LaunchCtx* lc) {
     unsigned int* err = nullptr;
     int rc = error_word_address(p.device, &err);
     if (rc != NA2D_OK) return rc;
-    *lc = na2d_tc::LaunchCtx{p.g, p.dtype, p.B, p.device, p.st, err, launched, p.dkdv_f32};
+    *lc = na2d_tc::LaunchCtx{p.g, p.dtype, p.B, p.device, p.st, err, launched, p.dkdv_f32, p.sm_margin};
     return NA2D_OK;
 }
 

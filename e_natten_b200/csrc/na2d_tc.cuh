@@ -385,7 +385,11 @@ struct LaunchCtx {
     unsigned int* err_word;
     int* launched;
     bool dkdv_f32;         // the dK/dV kernel writes fp32 (partial sums of a row band)
+    int sm_margin;         // SMs to leave free for a kernel that runs beside this one
 };
+
+// CTAs of a persistent launch over `tiles` tiles.
+inline int persistent_grid(const LaunchCtx& lc, long long tiles);
 
 // Register re-balancing of the 384-thread kernels (launched with 168 registers per thread): the
 // four warps of the data-movement group shrink to kRegsDonor, the eight softmax warps grow to
@@ -403,6 +407,12 @@ static_assert((kDkvRegsSoftmax - kDkvRegsLaunch) * 8 <= (kDkvRegsLaunch - kDkvRe
 constexpr int kSmemLimit = 232448;     // dynamic shared memory a CTA can opt in to on sm_100
 
 // Number of SMs of `device` (persistent kernels launch one CTA per SM), cached.
+inline int sm_count(int device);
+inline int persistent_grid(const LaunchCtx& lc, long long tiles) {
+    int sms = sm_count(lc.device) - lc.sm_margin;
+    if (sms < 1) sms = 1;
+    return (int)(tiles < sms ? tiles : sms);
+}
 inline int sm_count(int device) {
     static std::mutex mu;
     static int cache[64];

@@ -509,7 +509,7 @@ int launch_dq(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, const
     auto kern = dq_kernel<DT, D, KS>;
     static std::atomic<unsigned long long> opted{0};
     if (opt_in_smem(kern, C::SMEM, lc.device, opted) != cudaSuccess) return NA2D_ERR_CUDA;
-    const int grid = (int)(tiles < sm_count(lc.device) ? tiles : sm_count(lc.device));
+    const int grid = persistent_grid(lc, tiles);
     kern<<<grid, 384, C::SMEM, lc.st>>>(tq, tg, tk, tv, tdq, lse, delta, delta_in, d_q.ptr != nullptr, lc.err_word, g,
                                         tiles_r, tiles_c, (int)tiles);
     *lc.launched += 1;

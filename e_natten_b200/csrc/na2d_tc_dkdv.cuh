@@ -602,7 +602,7 @@ int launch_dkdv(const LaunchCtx& lc, const TensorArg& q, const TensorArg& k, con
     auto kern = dkdv_kernel<DT, D, KS>;
     static std::atomic<unsigned long long> opted{0};
     if (opt_in_smem(kern, C::SMEM, lc.device, opted) != cudaSuccess) return NA2D_ERR_CUDA;
-    const int grid = (int)(tiles < sm_count(lc.device) ? tiles : sm_count(lc.device));
+    const int grid = persistent_grid(lc, tiles);
     kern<<<grid, 512, C::SMEM, lc.st>>>(tk, tv, tq, tg, tdk, tdv, lse, delta, lc.dkdv_f32 ? 1 : 0, lc.err_word, g,
                                         tiles_r, tiles_c, (int)tiles);
     *lc.launched += 1;

@@ -143,9 +143,12 @@ def _args(like, kernel_size: int, rows, path: str, scale: float, **tensors) -> _
 
 
 # ---- raw launches into caller-owned buffers ------------------------------------------------------------
-def forward_into(q, k, v, o, lse, kernel_size: int, rows=None, path: str = "auto", scale: float = 1.0) -> None:
-    """Launch the forward into caller-owned ``o`` / ``lse``; nothing is allocated."""
+def forward_into(q, k, v, o, lse, kernel_size: int, rows=None, path: str = "auto", scale: float = 1.0,
+                 sm_margin: int = 0) -> None:
+    """Launch the forward into caller-owned ``o`` / ``lse``; nothing is allocated.  ``sm_margin``
+    SMs are left free for a kernel that should run beside this one (a halo exchange)."""
     a = _args(q, kernel_size, rows, path, scale, q=q, k=k, v=v, o=o, lse=lse)
+    a.flags |= _lib.flag_sm_margin(sm_margin)
     _lib.check(_lib.lib.na2d_forward_ex(C.byref(a)))
 
 
@@ -158,7 +161,7 @@ def backward_dq_into(q, k, v, o, lse, d_o, d_q, delta, kernel_size: int, rows=No
 
 
 def backward_dkdv_into(q, k, v, lse, d_o, delta, d_k, d_v, kernel_size: int, rows=None, path: str = "auto",
-                       scale: float = 1.0) -> None:
+                       scale: float = 1.0, sm_margin: int = 0) -> None:
     """Launch the key half of the backward: reads ``delta``, writes ``d_k`` and ``d_v``, which have
     the inputs' dtype or, for 16-bit inputs, may both be fp32 (partial sums of a row band)."""
     a = _args(q, kernel_size, rows, path, scale, q=q, k=k, v=v, lse=lse, d_o=d_o, delta=delta, d_k=d_k, d_v=d_v)
@@ -166,6 +169,7 @@ def backward_dkdv_into(q, k, v, lse, d_o, delta, d_k, d_v, kernel_size: int, row
         if d_k.dtype != torch.float32 or d_v.dtype != torch.float32:
             raise ValueError("d_k and d_v must have the inputs' dtype or both be float32")
         a.flags |= _lib.FLAG_DKDV_F32
+    a.flags |= _lib.flag_sm_margin(sm_margin)
     _lib.check(_lib.lib.na2d_backward_dkdv_ex(C.byref(a)))
 
 

@@ -39,6 +39,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Tuple
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -111,13 +113,55 @@ def _partial_dtype(dtype: torch.dtype) -> torch.dtype:
     return torch.float32 if dtype in (torch.bfloat16, torch.float16) else dtype
 
 
+_TILE_ROWS = 16      # rows of a kernel tile: launches over whole tiles waste no tile rows
+
+
+def _up16(n: int) -> int:
+    return (n + _TILE_ROWS - 1) // _TILE_ROWS * _TILE_ROWS
+
+
+def _query_strips(shard: RowShard) -> Tuple[int, int]:
+    """(a, b): the band's query rows [a, b) run before the halo has arrived, [0, a) and [b, R)
+    after it.  Rows [0, top) and [R - bot, R) are the ones that need halo rows; the strips are
+    widened to whole tiles where the band is tall enough, so that the three launches together
+    cover no more tile rows than one launch over the band would."""
+    R, a, b = shard.R, shard.top, shard.bot
+    wa, wb = (_up16(a) if a else 0), (_up16(b) if b else 0)
+    if wa + wb <= R:
+        a, b = wa, wb
+    return a, R - b
+
+
+def _key_strips(shard: RowShard) -> Tuple[int, int, int, int]:
+    """(own_top, own_bot, n_up, n_dn): the key half's top strip covers the upper halo rows and
+    the first own_top own rows, its bottom strip the last own_bot own rows and the lower halo rows;
+    the neighbours' partials arrive for the first n_up and the last n_dn own rows (own_top >= n_up,
+    own_bot >= n_dn).  The strips are widened to whole tiles where the band is tall enough."""
+    up, dn = _neighbours(shard)
+    n_up = up.bot if up is not None else 0
+    n_dn = dn.top if dn is not None else 0
+    own_top, own_bot = n_up, n_dn
+    wt = _up16(shard.top + n_up) - shard.top if shard.top + n_up > 0 else 0
+    wb = _up16(shard.bot + n_dn) - shard.bot if shard.bot + n_dn > 0 else 0
+    if wt + wb <= shard.R:
+        own_top, own_bot = wt, wb
+    return own_top, own_bot, n_up, n_dn
+
+
 class RowShardWorkspace:
     """The buffers of one rank that outlive a step: extended K / V (own rows in the middle, halo
     rows around them), and the fp32 extended dK / dV with the receive buffers of their reduction.
     ``k_local`` / ``v_local`` are views of the middle rows: K / V written there need no copy."""
 
-    def __init__(self, shard: RowShard, B: int, N: int, W: int, C: int, dtype: torch.dtype, device):
+    def __init__(self, shard: RowShard, B: int, N: int, W: int, C: int, dtype: torch.dtype, device,
+                 sm_margin: Optional[int] = None):
         self.shard = shard
+        # SMs the launches that run beside an exchange leave to NCCL's copy kernels: the persistent
+        # kernels otherwise hold every SM (and nearly all of its shared memory) until they end, and
+        # the transfer that was meant to run under them runs after them
+        if sm_margin is None:
+            sm_margin = int(os.environ.get("NA2D_SHARD_SM_MARGIN", "16"))
+        self.sm_margin = sm_margin if shard.world > 1 else 0
         shape = (B, N, shard.Hkv, W, C)
         self.k_ext = torch.empty(shape, dtype=dtype, device=device)
         self.v_ext = torch.empty(shape, dtype=dtype, device=device)
@@ -143,11 +187,9 @@ class RowShardWorkspace:
             sh = self.shard
             B, N, _, W, C = self._shape
             pd = _partial_dtype(self._dtype)
-            up, dn = _neighbours(sh)
-            n_up = up.bot if up is not None else 0
-            n_dn = dn.top if dn is not None else 0
+            own_top, own_bot, n_up, n_dn = _key_strips(sh)
             mk = lambda rows: [torch.empty((B, N, rows, W, C), dtype=pd, device=self._device) for _ in range(2)] if rows > 0 else None
-            self._edges = {"top": mk(sh.top + n_up), "bot": mk(sh.bot + n_dn), "recv_up": mk(n_up), "recv_dn": mk(n_dn)}
+            self._edges = {"top": mk(sh.top + own_top), "bot": mk(sh.bot + own_bot), "recv_up": mk(n_up), "recv_dn": mk(n_dn)}
         return self._edges
 
     def partial_buffers(self):
@@ -262,16 +304,16 @@ def forward_band_into(ws: RowShardWorkspace, q, o, lse, kernel_size: int, group=
     query rows meanwhile and the two boundary strips once the halo is there.  No autograd."""
     sh = ws.shard
     reqs = start_kv_halo_exchange(ws.k_ext, ws.v_ext, sh, group)
-    a, b = sh.top, sh.R - sh.bot
+    a, b = _query_strips(sh)
     spans = [(a, b)]
 
-    def run(lo, hi):
+    def run(lo, hi, sm_margin=0):
         part = torch.empty(lse.shape[:2] + (hi - lo, lse.shape[3]), dtype=torch.float32, device=lse.device)
         F.forward_into(q[:, :, lo:hi], ws.k_ext, ws.v_ext, o[:, :, lo:hi], part, kernel_size, rows=sh.rows(lo, hi),
-                       path=path, scale=scale)
+                       path=path, scale=scale, sm_margin=sm_margin)
         return part
 
-    parts = [run(a, b)]
+    parts = [run(a, b, ws.sm_margin if reqs else 0)]
     finish_exchange(reqs)
     if a > 0:
         spans.append((0, a))
@@ -296,21 +338,20 @@ def backward_band_into(ws: RowShardWorkspace, q, o, lse, d_o, d_q, d_k, d_v, del
     sh = ws.shard
     up, dn = _neighbours(sh)
     top, bot, R = sh.top, sh.bot, sh.R
-    n_up = up.bot if up is not None else 0          # own first rows that rank - 1 also contributes to
-    n_dn = dn.top if dn is not None else 0
+    own_top, own_bot, n_up, n_dn = _key_strips(sh)
     F.backward_dq_into(q, ws.k_ext, ws.v_ext, o, lse, d_o, d_q, delta, kernel_size, rows=sh.rows(), path=path, scale=scale)
     edges = ws.edge_buffers()
 
-    def key_half(ext_lo, ext_hi, dk, dv):
+    def key_half(ext_lo, ext_hi, dk, dv, sm_margin=0):
         rows = F.make_rows(sh.row0, R, sh.kv_row0 + ext_lo, ext_hi - ext_lo, sh.H)
         F.backward_dkdv_into(q, ws.k_ext[:, :, ext_lo:ext_hi], ws.v_ext[:, :, ext_lo:ext_hi], lse, d_o, delta, dk, dv,
-                             kernel_size, rows=rows, path=path, scale=scale)
+                             kernel_size, rows=rows, path=path, scale=scale, sm_margin=sm_margin)
 
     # edge strips first, so that their partials are on their way while the interior runs
-    if top + n_up > 0:
-        key_half(0, top + n_up, edges["top"][0], edges["top"][1])
-    if bot + n_dn > 0:
-        key_half(top + R - n_dn, sh.Hkv, edges["bot"][0], edges["bot"][1])
+    if top + own_top > 0:
+        key_half(0, top + own_top, edges["top"][0], edges["top"][1])
+    if bot + own_bot > 0:
+        key_half(top + R - own_bot, sh.Hkv, edges["bot"][0], edges["bot"][1])
     ops = []
     for i in range(2):
         if up is not None:
@@ -320,18 +361,26 @@ def backward_band_into(ws: RowShardWorkspace, q, o, lse, d_o, d_q, d_k, d_v, del
                 ops += [dist.P2POp(dist.irecv, s, _peer(group, sh.rank - 1), group) for s in _slabs(edges["recv_up"][i], slice(0, n_up))]
         if dn is not None:
             if bot > 0:
-                ops += [dist.P2POp(dist.isend, s, _peer(group, sh.rank + 1), group) for s in _slabs(edges["bot"][i], slice(n_dn, n_dn + bot))]
+                ops += [dist.P2POp(dist.isend, s, _peer(group, sh.rank + 1), group)
+                        for s in _slabs(edges["bot"][i], slice(own_bot, own_bot + bot))]
             if n_dn > 0:
                 ops += [dist.P2POp(dist.irecv, s, _peer(group, sh.rank + 1), group) for s in _slabs(edges["recv_dn"][i], slice(0, n_dn))]
     reqs = dist.batch_isend_irecv(ops) if ops else []
-    if R - n_up - n_dn > 0:
-        key_half(top + n_up, top + R - n_dn, d_k[:, :, n_up:R - n_dn], d_v[:, :, n_up:R - n_dn])
+    if R - own_top - own_bot > 0:
+        key_half(top + own_top, top + R - own_bot, d_k[:, :, own_top:R - own_bot], d_v[:, :, own_top:R - own_bot],
+                 ws.sm_margin if reqs else 0)
     finish_exchange(reqs)
     for i, out in enumerate((d_k, d_v)):
-        if n_up > 0:
-            out[:, :, :n_up] = edges["top"][i][:, :, top:] + edges["recv_up"][i]
-        if n_dn > 0:
-            out[:, :, R - n_dn:] = edges["bot"][i][:, :, :n_dn] + edges["recv_dn"][i]
+        if own_top > 0:
+            own = edges["top"][i][:, :, top:]                       # the strip's own rows, fp32
+            if n_up > 0:
+                own[:, :, :n_up] += edges["recv_up"][i]
+            out[:, :, :own_top] = own
+        if own_bot > 0:
+            own = edges["bot"][i][:, :, :own_bot]
+            if n_dn > 0:
+                own[:, :, own_bot - n_dn:] += edges["recv_dn"][i]
+            out[:, :, R - own_bot:] = own
 
 
 def _default_forward(q, k_ext, v_ext, ks, rows):
@@ -357,7 +406,7 @@ class RowShardedNatten2d(torch.autograd.Function):
                 ext_local.copy_(t)                     # K / V built elsewhere: one copy into the middle rows
         reqs = start_kv_halo_exchange(ws.k_ext, ws.v_ext, shard, group)
         # interior query rows see no halo row: their forward runs while the halo is on its way
-        a, b = shard.top, R - shard.bot
+        a, b = _query_strips(shard)
         parts = [None, fwd(q[:, :, a:b], ws.k_ext, ws.v_ext, kernel_size, shard.rows(a, b)), None]
         finish_exchange(reqs)
         if a > 0:

@@ -156,7 +156,7 @@ int na2d_backward(const void* q, const void* k, const void* v, const void* o, co
  *   flags     NA2D_FLAG_DKDV_F32: the key half writes dK and dV in fp32.  Meant for row views: the
  *             dK / dV of a band are partial sums that their owner adds to its own, and partial
  *             sums can be far larger than the total, so rounding each of them to 16 bits first
- *             costs accuracy.
+ *             costs accuracy.  NA2D_FLAG_SM_MARGIN(n): leave n SMs to a concurrent kernel.
  *   lse       fp32 (B, N, Hq, W), dense: written by the forward, read by the backward.
  *   delta     fp32 (B, N, Hq, W), dense scratch of the backward.
  */
@@ -172,6 +172,11 @@ typedef enum na2d_op {
 
 /* na2d_args.flags */
 #define NA2D_FLAG_DKDV_F32 1   /* d_k, d_v are fp32 tensors (strides in fp32 elements) whatever `dtype` is */
+/* Bits 8..15: SMs to leave free.  The tensor-core kernels are persistent, one CTA per SM, and a CTA
+ * takes nearly all of an SM's shared memory: a communication kernel launched beside them (the halo
+ * exchange of the row-sharded mode) finds no SM until they end.  A launch that should overlap with
+ * one asks for n fewer CTAs.  0 = use every SM. */
+#define NA2D_FLAG_SM_MARGIN(n) (((n) & 0xff) << 8)
 
 typedef struct na2d_args {
     size_t struct_size;

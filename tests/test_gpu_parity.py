@@ -502,6 +502,28 @@ def test_layouts_the_tensor_maps_cannot_take_are_copied():
 
 
 # ------------------------------------------------------------------------------ bounded waits
+def test_sm_margin_changes_the_grid_not_the_result():
+    """NA2D_FLAG_SM_MARGIN: the persistent kernels launch on fewer SMs (to leave room for a halo
+    exchange running beside them); the outputs are bit-identical."""
+    dtype, ks, shape = torch.bfloat16, 7, (1, 2, 70, 90, 64)
+    q, k, v, d_o = (t.to(DEV) for t in make_inputs(shape, dtype, 5, q_scale=0.125))
+    outs = []
+    for margin in (0, 16, 147, 255):
+        o = torch.empty_like(q)
+        lse = torch.empty(shape[:4], dtype=torch.float32, device=DEV)
+        na.functional.forward_into(q, k, v, o, lse, ks, sm_margin=margin)
+        delta = torch.empty_like(lse)
+        dq = torch.empty_like(q)
+        na.functional.backward_dq_into(q, k, v, o, lse, d_o, dq, delta, ks)
+        dk, dv = torch.empty_like(k), torch.empty_like(v)
+        na.functional.backward_dkdv_into(q, k, v, lse, d_o, delta, dk, dv, ks, sm_margin=margin)
+        na.check_kernels(DEV)
+        outs.append((o, lse, dk, dv))
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert torch.equal(a, b)
+
+
 def test_bounded_wait_gives_up_and_is_reported_once():
     """A wait that nothing ever satisfies ends by itself: the self-test kernel waits 2 ms on a
     barrier nobody completes, records that, and exits normally.  na2d_check reports it once and

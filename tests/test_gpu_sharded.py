@@ -71,12 +71,22 @@ def _worker(rank, world, port, shape, ks, dtype, result):
                                             ((2, 2, 40, 24, 128), 5, torch.bfloat16),     # strip kernels
                                             ((1, 2, 36, 40, 64), 3, torch.float16)])
 def test_row_sharded_two_gpus(shape, ks, dtype):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    _run_world(2, shape, ks, dtype)
+
+
+@pytest.mark.parametrize("shape,ks,dtype", [((1, 2, 144, 24, 64), 7, torch.bfloat16),      # whole-tile strips on both sides
+                                            ((1, 2, 60, 40, 128), 5, torch.bfloat16)])     # bands too short for them
+def test_row_sharded_three_gpus_middle_rank_has_two_neighbours(shape, ks, dtype):
+    _run_world(3, shape, ks, dtype)
+
+
+def _run_world(world, shape, ks, dtype):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     result = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, shape, ks, dtype, result)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, shape, ks, dtype, result)) for r in range(world)]
     for p in procs:
         p.start()
     deadline = time.time() + 240
@@ -89,4 +99,4 @@ def test_row_sharded_two_gpus(shape, ks, dtype):
             p.kill()
         p.join()
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
-    assert result.get(timeout=5) == [True, True]
+    assert result.get(timeout=5) == [True] * world
