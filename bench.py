@@ -79,8 +79,8 @@ def algorithmic_bytes(B, N, H, W, C, esize):
 
 # DRAM bytes (read + written) per launch of the three kernels on the headline workload, from an ncu
 # capture of that workload itself (dram__bytes_read.sum + dram__bytes_write.sum, one launch each).
-NCU_DRAM_BYTES = {"c2-256": {"na2d forward": 805445632 + 248020736, "na2d backward dQ": 1078204416 + 249562368,
-                             "na2d backward dK/dV": 1082870016 + 499711744}}
+NCU_DRAM_BYTES = {"c2-256": {"na2d forward": 806513920 + 248424448, "na2d backward dQ": 1088127232 + 250111744,
+                             "na2d backward dK/dV": 1086513408 + 500653056}}
 NCU_TRAFFIC_SOURCE = "ncu capture of this workload (c2-256), one launch per kernel"
 
 
