@@ -175,3 +175,92 @@ def test_row_sharding_inside_a_subgroup_that_does_not_start_at_rank_0():
         p.join(timeout=180)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert result.get(timeout=5) < 1e-12
+
+
+# ---- the band path the GPU runs (whole-tile strips, fp32 edge partials, overlapped exchanges) --------------
+def _band_worker(rank, world, port, H, W, ks, result):
+    """forward_band_into / backward_band_into with the three launches replaced by the CPU oracle: what
+    is under test is which rows each launch gets, what travels, and how the edge strips are put
+    back together."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        q, k, v, d_o = orc.round_inputs((1, 2, H, W, 3), torch.float64, 29)
+        sh = sharding.plan_row_shard(H, world, rank, ks)
+        band = slice(sh.row0, sh.row0 + sh.R)
+        ws = sharding.RowShardWorkspace(sh, 1, 2, W, 3, torch.float64, "cpu")
+        ws.k_local.copy_(k[:, :, band])
+        ws.v_local.copy_(v[:, :, band])
+        calls = []
+
+        def view(rows):
+            return (rows.q_row0, rows.kv_row0, rows.H_global)
+
+        def forward_into(qv, k_ext, v_ext, o, lse, kernel_size, rows=None, path="auto", scale=1.0, sm_margin=0):
+            calls.append(("fwd", rows.q_row0 - sh.row0, rows.Hq, sm_margin))
+            ro, rl = orc.natten2d_fwd(qv, k_ext, v_ext, kernel_size, rows=view(rows))
+            o.copy_(ro)
+            lse.copy_(rl)
+
+        def backward_dq_into(qv, k_ext, v_ext, o, lse, g, d_q, delta, kernel_size, rows=None, path="auto", scale=1.0):
+            dq, _, _ = orc.natten2d_bwd(qv, k_ext, v_ext, g, kernel_size, rows=view(rows))
+            d_q.copy_(dq)
+
+        def backward_dkdv_into(qv, k_sub, v_sub, lse, g, delta, d_k, d_v, kernel_size, rows=None, path="auto",
+                               scale=1.0, sm_margin=0):
+            # the key band of this call is a part of the extended rows: take that part of the full result
+            lo = rows.kv_row0 - sh.kv_row0
+            calls.append(("dkdv", lo, rows.Hkv, sm_margin))
+            full = sharding.F.make_rows(sh.row0, sh.R, sh.kv_row0, sh.Hkv, sh.H)
+            _, dk, dv = orc.natten2d_bwd(qv, ws.k_ext, ws.v_ext, g, kernel_size, rows=view(full))
+            d_k.copy_(dk[:, :, lo:lo + rows.Hkv])
+            d_v.copy_(dv[:, :, lo:lo + rows.Hkv])
+
+        sharding.F.forward_into = forward_into
+        sharding.F.backward_dq_into = backward_dq_into
+        sharding.F.backward_dkdv_into = backward_dkdv_into
+        ql, gl = q[:, :, band].contiguous(), d_o[:, :, band].contiguous()
+        o = torch.empty_like(ql)
+        lse = torch.empty(ql.shape[:4], dtype=torch.float32)
+        sharding.forward_band_into(ws, ql, o, lse, ks)
+        d_q, d_k, d_v = (torch.full_like(ql, float("nan")) for _ in range(3))
+        delta = torch.empty_like(lse)
+        sharding.backward_band_into(ws, ql, o, lse, gl, d_q, d_k, d_v, delta, ks)
+        ro, _, rdq, rdk, rdv = orc.natten2d_fwd_bwd(q, k, v, d_o, ks)
+        err = max((o - ro[:, :, band]).abs().max().item(), (d_q - rdq[:, :, band]).abs().max().item(),
+                  (d_k - rdk[:, :, band]).abs().max().item(), (d_v - rdv[:, :, band]).abs().max().item())
+        out = [None] * world
+        dist.all_gather_object(out, (err, calls))
+        if rank == 0:
+            result.put(out)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,H,W,ks,whole_tiles", [(3, 144, 9, 7, True), (3, 60, 8, 5, False), (2, 96, 14, 13, True)])
+def test_band_path_strips_and_partials_reassemble(world, H, W, ks, whole_tiles):
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_band_worker, args=(r, world, port, H, W, ks, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    out = result.get(timeout=5)
+    assert max(e for e, _ in out) < 1e-12
+    R = H // world
+    for rank, (_, calls) in enumerate(out):
+        fwd = [c for c in calls if c[0] == "fwd"]
+        dkdv = [c for c in calls if c[0] == "dkdv"]
+        sides = (rank > 0) + (rank < world - 1)
+        assert len(fwd) == 1 + sides and len(dkdv) == 1 + sides
+        # the launch that runs beside an exchange leaves SMs free; the strips after it do not
+        assert fwd[0][3] > 0 and all(c[3] == 0 for c in fwd[1:])
+        assert sum(c[2] for c in fwd) == R                       # every query row exactly once
+        if whole_tiles:
+            assert all(c[2] == 16 for c in fwd[1:])              # whole-tile strips
+            assert all(c[2] == 16 for c in dkdv[:-1])
+        elif sides == 2:
+            assert all(c[2] == ks // 2 for c in fwd[1:])         # a band too short for two whole-tile strips
