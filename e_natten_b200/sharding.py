@@ -332,9 +332,11 @@ def backward_band_into(ws: RowShardWorkspace, q, o, lse, d_o, d_q, d_k, d_v, del
     dQ comes from one launch over the band.  The key half runs in up to three launches over parts
     of the extended key rows: the interior key rows - every query that sees them is local - go
     straight into ``d_k`` / ``d_v`` in the tensors' dtype; the two edge strips (the halo rows this
-    rank computed for its neighbours, and its own rows that the neighbours' queries see as well) are
-    partial sums and go into small fp32 buffers.  The halo partials are sent to their owners, what
-    arrives is added to the own edge rows, and those are rounded once into ``d_k`` / ``d_v``."""
+    rank computed for its neighbours, and its own rows next to them - at least those the neighbours'
+    queries see as well, widened to a whole tile of rows where the band is tall enough) go into
+    small fp32 buffers.  The halo partials are sent to their owners, what arrives is added to the
+    own edge rows, and those are rounded once into ``d_k`` / ``d_v``.  The interior launch, which
+    runs while the partials travel, leaves ``ws.sm_margin`` SMs to the transfer."""
     sh = ws.shard
     up, dn = _neighbours(sh)
     top, bot, R = sh.top, sh.bot, sh.R
